@@ -3,9 +3,12 @@ and slots for per-request state of fixed size.
 
 What a mixer keeps between steps is declared as a *need*:
   PagedKVNeed(n_kv_heads, head_dim, window)  keys and values of every token (window=None) or of
-                                             the last `window` tokens only
+                                             the last `window` tokens only; with `keep_first` = F also
+                                             of the first F tokens, whose pages a window never gives back
   StateNeed(shape, dtype)                    an array of fixed size per request
-Caches whose needs differ in kind (all keys / a window of them) form groups with pages of their
+A mixer that keeps several things (keys and values beside a recurrent state, say) declares a tuple of
+needs; the caches of run `c` are then named (c, 0), (c, 1), ... .
+Caches whose needs differ in kind (all keys / a window of them / a window and the first tokens) form groups with pages of their
 own: a page id of a group indexes the K and V arrays of every cache in that group, and each
 group has its own pool and its own block table per request.  A request owns one slot (a row in
 every block table and in every state array) from `open` to `close`.
@@ -39,6 +42,8 @@ class PagedKVNeed:
     head_dim: int
     window: Optional[int] = None
     q_heads: int = 0                 # hint for work splitting only
+    keep_first: int = 0              # with a window: the first tokens of a request stay readable too
+    library: Optional[str] = "attention"      # the kernel library that reads the cache (built before the first step)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -51,11 +56,19 @@ class OutOfSlots(RuntimeError):
     pass
 
 
+def cache_id_key(cid) -> Tuple[int, int]:
+    """Order of cache ids: a run's id `c`, or (c, k) for the k-th need of a mixer that declares several."""
+    return (cid[0], cid[1]) if isinstance(cid, tuple) else (cid, -1)
+
+
 class KVGroup:
     """Caches with the same kind of need: one pool, one block table per request."""
 
-    def __init__(self, window: Optional[int], num_pages: int, max_reqs: int, max_pages_per_req: int):
+    def __init__(self, window: Optional[int], num_pages: int, max_reqs: int, max_pages_per_req: int, keep_first: int = 0,
+                 page_size: int = 1):
         self.window = window
+        self.keep_first = keep_first if window is not None else 0
+        self.keep_pages = -(-self.keep_first // page_size)        # leading pages that a window never gives back
         self.pool = PagePool(num_pages)
         self.table = np.zeros((max_reqs + 1, max_pages_per_req), dtype=np.int32)
         self.n_pages = np.zeros(max_reqs + 1, dtype=np.int64)      # table entries in use (released ones included)
@@ -76,23 +89,26 @@ class CacheManager:
         self.needs = dict(needs)
         self.groups: List[KVGroup] = []
         self.group_of_cache: Dict[int, int] = {}
-        by_window: Dict[Optional[int], int] = {}
-        for cid in sorted(needs):
+        by_window: Dict[Tuple[Optional[int], int], int] = {}
+        for cid in sorted(needs, key=cache_id_key):
             need = needs[cid]
             if isinstance(need, PagedKVNeed):
                 if need.window is not None and need.window < 1:
                     raise ValueError("a window must be at least 1 token")
-                if need.window not in by_window:
+                if need.keep_first < 0:
+                    raise ValueError("keep_first must not be negative")
+                kind = (need.window, need.keep_first if need.window is not None else 0)
+                if kind not in by_window:
                     n = num_pages
                     if need.window is not None:
-                        per_req = -(-(need.window + max(max_step_tokens, 1)) // page_size) + 2
+                        per_req = -(-(need.window + max(max_step_tokens, 1)) // page_size) + 2 + -(-kind[1] // page_size)
                         n = min(num_pages, max_reqs * per_req)
-                    by_window[need.window] = len(self.groups)
-                    self.groups.append(KVGroup(need.window, n, max_reqs, self.max_pages_per_req))
-                g = by_window[need.window]
+                    by_window[kind] = len(self.groups)
+                    self.groups.append(KVGroup(need.window, n, max_reqs, self.max_pages_per_req, kind[1], page_size))
+                g = by_window[kind]
                 self.groups[g].cache_ids.append(cid)
                 self.group_of_cache[cid] = g
-        self.state_ids = [cid for cid in sorted(needs) if isinstance(needs[cid], StateNeed)]
+        self.state_ids = [cid for cid in sorted(needs, key=cache_id_key) if isinstance(needs[cid], StateNeed)]
         self._free_slots = deque(range(1, max_reqs + 1))           # slot 0: dump row for padded batch rows
         self._open = np.zeros(max_reqs + 1, dtype=bool)
         self.length = np.zeros(max_reqs + 1, dtype=np.int64)       # tokens committed
@@ -198,7 +214,7 @@ class CacheManager:
                 continue
             dead = max(0, (new_len - g.window + 1) // P)       # pages wholly before the next query's window
             dead = min(dead, int(g.n_pages[slot]))
-            first = int(g.first_live[slot])
+            first = max(int(g.first_live[slot]), g.keep_pages)   # the pages of the kept first tokens stay
             if dead > first:
                 g.pool.free(int(p) for p in g.table[slot, first:dead])
                 g.table[slot, first:dead] = 0
@@ -207,8 +223,10 @@ class CacheManager:
 
     def owned_pages(self, slot: int, group: int = 0) -> List[int]:
         g = self.groups[group]
+        hi = int(g.n_pages[slot])
         lo = max(int(g.first_live[slot]), int(self.borrowed[slot]) if group == 0 else 0)
-        return [int(p) for p in g.table[slot, lo:int(g.n_pages[slot])]]
+        kept = range(0, min(g.keep_pages, lo, hi)) if g.first_live[slot] > 0 else range(0)
+        return [int(g.table[slot, i]) for i in kept] + [int(p) for p in g.table[slot, lo:hi]]
 
     def close(self, slot: int, keep_pages: int = 0) -> None:
         """Give back the slot and every page the request owns; `keep_pages` leading owned pages of
@@ -217,9 +235,11 @@ class CacheManager:
             raise ValueError(f"slot {slot} closed twice")
         for gi, g in enumerate(self.groups):
             lo = int(g.first_live[slot])
+            hi = int(g.n_pages[slot])
+            if lo > 0 and g.keep_pages:                         # a window has given pages back, but never the first ones
+                g.pool.free(int(p) for p in g.table[slot, 0:min(g.keep_pages, lo, hi)])
             if gi == 0:
                 lo = max(lo, int(self.borrowed[slot]) + keep_pages)
-            hi = int(g.n_pages[slot])
             if hi > lo:
                 g.pool.free(int(p) for p in g.table[slot, lo:hi])
             g.table[slot, :hi] = 0

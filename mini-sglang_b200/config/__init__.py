@@ -1,7 +1,9 @@
 from .registry import ARCHITECTURES, ConfigError, architecture_of, load_config, read_config_json, register_architecture
 from .spec import LayerSpec, ModelSpec, PartSpec, Run
 from . import qwen3 as _qwen3  # registers "Qwen3ForCausalLM"
+from . import vekurax as _vekurax  # registers "Vekurax"
 from .qwen3 import Qwen3Config
+from .vekurax import VekuraxConfig
 
 __all__ = ["ARCHITECTURES", "ConfigError", "architecture_of", "load_config", "read_config_json",
-           "register_architecture", "LayerSpec", "ModelSpec", "PartSpec", "Run", "Qwen3Config"]
+           "register_architecture", "LayerSpec", "ModelSpec", "PartSpec", "Run", "Qwen3Config", "VekuraxConfig"]

@@ -46,6 +46,8 @@ def read_config_json(model_dir: str) -> Dict[str, Any]:
 
 def architecture_of(raw: Dict[str, Any]) -> Architecture:
     names = raw.get("architectures") or []
+    if not names and isinstance(raw.get("architecture"), str):
+        names = [raw["architecture"]]          # some designs name themselves with one string
     if not names:
         raise ConfigError("config.json has no `architectures` entry; known: " + ", ".join(sorted(ARCHITECTURES)))
     if names[0] not in ARCHITECTURES:

@@ -35,7 +35,7 @@ class LayerSpec:
 
     prefix: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]      # None: the block has no feed-forward (arrangements that allow it)
     norms: Dict[str, PartSpec]
     position: Optional[PartSpec] = None
     block: str = "prenorm_residual"

@@ -1,0 +1,566 @@
+// Kernels of the mixers, norms and activations beyond the rotary softmax attention of attention.cu:
+//
+//   dyntanh_kernel              y = tanh(alpha * (residual + x)) * w + b, the sum kept in the float32 stream
+//   conv_norm_kvwrite_kernel    short causal convolution over time on q and k (carried per request in a state of the
+//                               last taps-1 inputs), RMS norm over the whole q and the whole k projection, k and the
+//                               un-normed k (the values) into the paged cache
+//   conv_state_update_kernel    the state of that convolution after the step
+//   window_attention_kernel     softmax attention over a sliding window plus the first tokens of the sequence, with a
+//                               bias looked up by distance and one output gate per head; float32 arithmetic, any head size
+//   decay_attention_kernel      linear attention with a fixed decay per head, S <- a S + k v^T, o = S^T q, the state in
+//                               float32 per request; walks a request's tokens in order (decode and short portions)
+//   decay_chunk_*_kernel        the same for long portions: chunks of a request in parallel, their sums scanned in order
+//   rms_gate_kernel             RMS norm over a row, times sigmoid(gate), times a constant
+//   gated_act_kernel            act(gate) * up with act = silu or tanh-gelu
+//
+// Element type T (float or bfloat16) is the type of activations and caches; every sum, norm, score, weight of the
+// softmax, decay and state is float32 in both.  Inputs that come out of a packed projection are addressed by a base
+// pointer, a row stride and a column offset, outputs that go into a packed operand of the next product likewise.
+#include "common.cuh"
+#include <math.h>
+
+#define MIX_MAX_TAPS 16
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float siluf_(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float gelu_tanhf_(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// ---------------------------------------------------------------------------------------
+// Dynamic Tanh norm
+// ---------------------------------------------------------------------------------------
+template <typename T, typename X>
+__global__ void dyntanh_kernel(const X* __restrict__ x, const float* __restrict__ res_in, float* __restrict__ res_out,
+                               const int* __restrict__ row_idx, const float* __restrict__ w, const float* __restrict__ b,
+                               float alpha, T* __restrict__ y, int H) {
+    const int i = blockIdx.x;
+    const size_t r = row_idx ? (size_t)row_idx[i] : (size_t)i;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = 0.f;
+        if (res_in) v = res_in[r * H + c];
+        if (x) v += to_f32<X>(x[r * H + c]);
+        if (res_out) res_out[r * H + c] = v;
+        y[(size_t)i * H + c] = from_f32<T>(tanhf(alpha * v) * w[c] + b[c]);
+    }
+}
+
+MSGL_API int msgl_dyntanh(const void* x, int x_is_f32, const float* res_in, float* res_out, const int* row_idx,
+                          const float* w, const float* b, float alpha, void* y, int rows, int H, int dtype,
+                          cudaStream_t stream) {
+    if (rows <= 0) return MSGL_OK;
+    if (H <= 0) return MSGL_ERR_SIZE;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (dtype == MSGL_F32)
+        dyntanh_kernel<float, float><<<rows, threads, 0, stream>>>((const float*)x, res_in, res_out, row_idx, w, b, alpha, (float*)y, H);
+    else if (dtype == MSGL_BF16 && x_is_f32)
+        dyntanh_kernel<__nv_bfloat16, float><<<rows, threads, 0, stream>>>((const float*)x, res_in, res_out, row_idx, w, b, alpha,
+                                                                             (__nv_bfloat16*)y, H);
+    else if (dtype == MSGL_BF16)
+        dyntanh_kernel<__nv_bfloat16, __nv_bfloat16><<<rows, threads, 0, stream>>>((const __nv_bfloat16*)x, res_in, res_out, row_idx, w, b,
+                                                                                     alpha, (__nv_bfloat16*)y, H);
+    else
+        return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// Short causal convolution on q and k + whole-projection RMS norm + cache write
+//
+//   proj row: q at column q_off (Cq = heads * d channels), k at column k_off (Ck = kv heads * d)
+//   y[t, c] = sum_j w[c, j] * u[t - taps + 1 + j, c]; inputs before this step's first token come from the
+//   request's state [slot][taps - 1][Cq + Ck] (oldest first; zero when the request was opened)
+//   q_out = rms(y_q) * wq_norm;  K cache <- rms(y_k) * wk_norm;  V cache <- y_k (before the norm)
+// One block per token.
+// ---------------------------------------------------------------------------------------
+struct ConvNormParams {
+    const void* proj; long long stride; int q_off, k_off;
+    int Cq, Ck, d, n_kv, taps;
+    const float* wq_conv; const float* wk_conv;      // [C, taps]
+    const float* wq_norm; const float* wk_norm;      // [C]
+    float eps;
+    void* state;                                     // [slots][taps - 1][Cq + Ck]
+    const int* token_req; const int* q_start; const int* slots; const int* out_loc;
+    void* q_out;                                     // [T, Cq]
+    void* k_cache; void* v_cache; int page_size;
+    int T;
+};
+
+template <typename T>
+__global__ void conv_norm_kvwrite_kernel(const ConvNormParams p) {
+    extern __shared__ float ybuf[];                  // [Cq + Ck]
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const int r = p.token_req[t];
+    const int t0 = p.q_start[r];
+    const int i = t - t0;                            // index of the token within the request's tokens of this step
+    const int slot = p.slots[r];
+    const int C = p.Cq + p.Ck, K = p.taps;
+    const T* proj = reinterpret_cast<const T*>(p.proj);
+    const T* st = reinterpret_cast<const T*>(p.state) + (size_t)slot * (K - 1) * C;
+    float ssq_q = 0.f, ssq_k = 0.f;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const bool is_q = c < p.Cq;
+        const int cc = is_q ? c : c - p.Cq;
+        const float* w = (is_q ? p.wq_conv : p.wk_conv) + (size_t)cc * K;
+        const int col = is_q ? p.q_off + cc : p.k_off + cc;
+        float acc = 0.f;
+        for (int j = 0; j < K; ++j) {
+            const int idx = i - (K - 1) + j;         // relative to the step's first token of this request
+            float u;
+            if (idx >= 0) u = to_f32<T>(proj[(size_t)(t0 + idx) * p.stride + col]);
+            else u = to_f32<T>(st[(size_t)(K - 1 + idx) * C + c]);
+            acc = fmaf(w[j], u, acc);
+        }
+        const float y = to_f32<T>(from_f32<T>(acc));  // as it leaves the convolution, in the activation type
+        ybuf[c] = y;
+        if (is_q) ssq_q += y * y; else ssq_k += y * y;
+    }
+    ssq_q = block_sum(ssq_q, red);
+    ssq_k = block_sum(ssq_k, red);
+    const float rq = 1.f / sqrtf(ssq_q / (float)p.Cq + p.eps), rk = 1.f / sqrtf(ssq_k / (float)p.Ck + p.eps);
+    __syncthreads();
+    T* qo = reinterpret_cast<T*>(p.q_out) + (size_t)t * p.Cq;
+    const int loc = p.out_loc ? p.out_loc[t] : 0;
+    const int page = loc / p.page_size, ps = loc - page * p.page_size;
+    T* kc = reinterpret_cast<T*>(p.k_cache);
+    T* vc = reinterpret_cast<T*>(p.v_cache);
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const float y = ybuf[c];
+        if (c < p.Cq) {
+            qo[c] = from_f32<T>(y * rq * p.wq_norm[c]);
+        } else if (kc) {
+            const int cc = c - p.Cq;
+            const int g = cc / p.d, e = cc - g * p.d;
+            const size_t a = (((size_t)page * p.n_kv + g) * p.page_size + ps) * p.d + e;
+            kc[a] = from_f32<T>(y * rk * p.wk_norm[cc]);
+            vc[a] = from_f32<T>(y);
+        }
+    }
+}
+
+template <typename T>
+__global__ void conv_state_update_kernel(const void* proj_, long long stride, int q_off, int k_off, int Cq, int Ck, int taps,
+                                         void* state_, const int* __restrict__ q_start, const int* __restrict__ slots) {
+    const int r = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int C = Cq + Ck, K = taps;
+    if (c >= C) return;
+    const int t0 = q_start[r], n = q_start[r + 1] - t0;
+    const int slot = slots[r];
+    const T* proj = reinterpret_cast<const T*>(proj_);
+    T* st = reinterpret_cast<T*>(state_) + (size_t)slot * (K - 1) * C;
+    const int col = c < Cq ? q_off + c : k_off + (c - Cq);
+    T keep[MIX_MAX_TAPS];
+#pragma unroll
+    for (int k = 0; k < MIX_MAX_TAPS; ++k) {
+        if (k < K - 1) {
+            const int idx = n - (K - 1) + k;         // index among this step's tokens of the request; negative: older
+            keep[k] = idx >= 0 ? proj[(size_t)(t0 + idx) * stride + col] : st[(size_t)(K - 1 + idx) * C + c];
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < MIX_MAX_TAPS; ++k)
+        if (k < K - 1) st[(size_t)k * C + c] = keep[k];
+}
+
+MSGL_API int msgl_conv_norm_kvwrite(const void* proj, long long stride, int q_off, int k_off, int Cq, int Ck, int d, int n_kv,
+                                    int taps, const float* wq_conv, const float* wk_conv, const float* wq_norm,
+                                    const float* wk_norm, float eps, void* state, const int* token_req, const int* q_start,
+                                    const int* slots, const int* out_loc, void* q_out, void* k_cache, void* v_cache,
+                                    int page_size, int T, int B, int dtype, cudaStream_t stream) {
+    if (T <= 0) return MSGL_OK;
+    if (taps < 1 || taps > MIX_MAX_TAPS || Cq <= 0 || Ck <= 0 || d <= 0 || Ck != n_kv * d) return MSGL_ERR_SIZE;
+    ConvNormParams p;
+    p.proj = proj; p.stride = stride; p.q_off = q_off; p.k_off = k_off; p.Cq = Cq; p.Ck = Ck; p.d = d; p.n_kv = n_kv; p.taps = taps;
+    p.wq_conv = wq_conv; p.wk_conv = wk_conv; p.wq_norm = wq_norm; p.wk_norm = wk_norm; p.eps = eps; p.state = state;
+    p.token_req = token_req; p.q_start = q_start; p.slots = slots; p.out_loc = out_loc; p.q_out = q_out;
+    p.k_cache = k_cache; p.v_cache = v_cache; p.page_size = page_size; p.T = T;
+    const size_t smem = (size_t)(Cq + Ck) * sizeof(float);
+    if (smem > 200 * 1024) return MSGL_ERR_SIZE;
+    const int threads = (Cq + Ck) >= 2048 ? 512 : 256;
+    static MsglOncePerDevice once_f, once_b;
+    if (dtype == MSGL_F32) {
+        if (smem > 48 * 1024 && once_f.due()) {
+            cudaFuncSetAttribute(conv_norm_kvwrite_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            once_f.mark();
+        }
+        conv_norm_kvwrite_kernel<float><<<T, threads, smem, stream>>>(p);
+        if (taps > 1)
+            conv_state_update_kernel<float><<<dim3(B, (Cq + Ck + 255) / 256), 256, 0, stream>>>(proj, stride, q_off, k_off, Cq, Ck, taps,
+                                                                                                 state, q_start, slots);
+    } else if (dtype == MSGL_BF16) {
+        if (smem > 48 * 1024 && once_b.due()) {
+            cudaFuncSetAttribute(conv_norm_kvwrite_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            once_b.mark();
+        }
+        conv_norm_kvwrite_kernel<__nv_bfloat16><<<T, threads, smem, stream>>>(p);
+        if (taps > 1)
+            conv_state_update_kernel<__nv_bfloat16><<<dim3(B, (Cq + Ck + 255) / 256), 256, 0, stream>>>(proj, stride, q_off, k_off, Cq, Ck,
+                                                                                                         taps, state, q_start, slots);
+    } else {
+        return MSGL_ERR_DTYPE;
+    }
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// Softmax attention over a window and the first tokens, with a bias by distance and an output gate
+//
+//   query at position i sees key j if j <= i and (i - j < window or j < keep_first)
+//   score = q . k * scale + bias[head][min(i - j, L - 1)]
+//   out[t, head, :] = softmax(score) V * sigmoid(gate[t, head]) * out_scale
+//
+// A block takes QT consecutive tokens of one request and GH query heads of one kv head: QT * GH <= 8 rows, one warp
+// each.  Keys go through shared memory in chunks of 32 anchored at multiples of 32, first the chunks that hold kept first
+// tokens before the window, then the window's, in rising order: the order of the sums at a position does not depend on
+// how the tokens were cut into steps.  In the score phase lane l of a row's warp takes key l of the chunk; in the value
+// phase lane l takes the output elements l, l + 32, ...
+// ---------------------------------------------------------------------------------------
+#define WA_ROWS 8
+#define WA_KC 32
+#define WA_MAX_DPL 16       // head sizes up to 512
+
+struct WindowAttnParams {
+    const void* q;            // [T, n_q, d]
+    const void* k_cache; const void* v_cache;
+    const int* q_start; const int* kv_len; const int* block_table; int bt_stride;
+    int uniform;                                  // every request brings one token: block x takes request x
+    const float* bias; int bias_len;              // [n_q][bias_len] or null
+    const void* gate; long long gate_stride; int gate_off;        // [T rows][.. n_q at gate_off] or null
+    void* out; long long out_stride; int out_off;                 // [T rows][.. n_q * d at out_off]
+    int B, n_q, n_kv, d, page_size, window, keep_first, QT, GH;
+    float scale, out_scale;
+};
+
+template <typename T, int DPL /* output elements per lane: head sizes up to 32 * DPL */>
+__global__ void __launch_bounds__(WA_ROWS * 32) window_attention_kernel(const WindowAttnParams p) {
+    extern __shared__ float smem[];
+    const int d = p.d;
+    float* qs = smem;                                // [WA_ROWS][d]
+    float* ks = qs + WA_ROWS * d;                    // [WA_KC][d + 1]
+    float* vs = ks + WA_KC * (d + 1);                // [WA_KC][d]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // block x is the x-th query tile of the step: tiles of QT tokens, request by request
+    __shared__ int tile_sh[2];
+    int req, t0;
+    if (p.uniform) {
+        req = blockIdx.x; t0 = 0;
+    } else {
+        if (tid == 0) {
+            int left = blockIdx.x, found = -1, at = 0;
+            for (int r = 0; r < p.B; ++r) {
+                const int nt = (p.q_start[r + 1] - p.q_start[r] + p.QT - 1) / p.QT;
+                if (left < nt) { found = r; at = left * p.QT; break; }
+                left -= nt;
+            }
+            tile_sh[0] = found; tile_sh[1] = at;
+        }
+        __syncthreads();
+        req = tile_sh[0]; t0 = tile_sh[1];
+    }
+    if (req < 0 || req >= p.B) return;
+    const int G = p.n_q / p.n_kv;
+    const int n_chunks = (G + p.GH - 1) / p.GH;
+    const int kvh = blockIdx.y / n_chunks, chunk = blockIdx.y - kvh * n_chunks;
+    const int q_base = p.q_start[req], q_len = p.q_start[req + 1] - q_base, kv_len = p.kv_len[req];
+    const int n_tok = min(p.QT, q_len - t0);
+    if (n_tok <= 0) return;
+    const int p_min = kv_len - q_len + t0, p_max = p_min + n_tok - 1;
+    const int window = p.window > 0 ? p.window : (1 << 30);
+    const int win_lo = max(0, p_min - window + 1);
+    const int sink_hi = min(p.keep_first, win_lo);                 // kept first tokens that lie before the tile's window
+    const int c_first = win_lo / WA_KC, c_last = p_max / WA_KC;
+    const int n_sink = min((sink_hi + WA_KC - 1) / WA_KC, c_first);
+    const int n_c = n_sink + (c_last - c_first + 1);
+
+    // this warp's row
+    const int tl = warp / p.GH, hl = warp - tl * p.GH;
+    const int hg = chunk * p.GH + hl;
+    const bool row_ok = tl < n_tok && hg < G && tl < p.QT;
+    const int head = kvh * G + (row_ok ? hg : 0);
+    const int tok = q_base + t0 + (row_ok ? tl : 0);
+    const int pos = p_min + tl;
+    const T* qg = reinterpret_cast<const T*>(p.q);
+    for (int e = lane; e < d; e += 32) qs[warp * d + e] = row_ok ? to_f32<T>(qg[((size_t)tok * p.n_q + head) * d + e]) : 0.f;
+    const float* bias = p.bias ? p.bias + (size_t)head * p.bias_len : nullptr;
+
+    const T* kc = reinterpret_cast<const T*>(p.k_cache);
+    const T* vc = reinterpret_cast<const T*>(p.v_cache);
+    const int* bt = p.block_table + (size_t)req * p.bt_stride;
+
+    float o[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) o[i] = 0.f;
+    float m = -INFINITY, l = 0.f;
+
+    for (int ci = 0; ci < n_c; ++ci) {
+        const int c = ci < n_sink ? ci : c_first + (ci - n_sink);
+        const int key0 = c * WA_KC;
+        __syncthreads();
+        // ---- the chunk's keys and values into shared memory (rows past the last key: zeros)
+        for (int idx = tid; idx < WA_KC * d; idx += WA_ROWS * 32) {
+            const int kr = idx / d, e = idx - kr * d;
+            const int key = key0 + kr;
+            float kv = 0.f, vv = 0.f;
+            if (key <= p_max) {
+                const int page = bt[key / p.page_size];
+                const size_t a = (((size_t)page * p.n_kv + kvh) * p.page_size + (key % p.page_size)) * d + e;
+                kv = to_f32<T>(kc[a]);
+                vv = to_f32<T>(vc[a]);
+            }
+            ks[kr * (d + 1) + e] = kv;
+            vs[kr * d + e] = vv;
+        }
+        __syncthreads();
+        // ---- score of key `lane`
+        const int key = key0 + lane;
+        const bool vis = row_ok && key <= pos && (pos - key < window || key < p.keep_first);
+        float s = -INFINITY;
+        if (vis) {
+            float acc = 0.f;
+            const float* qr = qs + warp * d;
+            const float* kr = ks + lane * (d + 1);
+            for (int e = 0; e < d; ++e) acc = fmaf(qr[e], kr[e], acc);
+            s = acc * p.scale;
+            if (bias) s += bias[min(pos - key, p.bias_len - 1)];
+        }
+        const float cmax = warp_max(s);
+        if (cmax == -INFINITY) continue;             // no key of this chunk is visible from this row (warp-uniform)
+        const float m_new = fmaxf(m, cmax);
+        const float alpha = (m == -INFINITY) ? 0.f : expf(m - m_new);
+        const float pr = vis ? expf(s - m_new) : 0.f;
+        l = l * alpha + pr;
+        m = m_new;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) o[i] *= alpha;
+        // ---- values
+        for (int j = 0; j < WA_KC; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, pr, j);
+            if (pj == 0.f) continue;                 // warp-uniform
+            const float* vr = vs + j * d;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) {
+                const int e = lane + 32 * i;
+                if (e < d) o[i] = fmaf(pj, vr[e], o[i]);
+            }
+        }
+    }
+    l = warp_sum(l);
+    if (!row_ok) return;
+    float f = (l > 0.f ? 1.f / l : 0.f) * p.out_scale;
+    if (p.gate) {
+        const T* gg = reinterpret_cast<const T*>(p.gate);
+        f *= sigmoidf_(to_f32<T>(gg[(size_t)tok * p.gate_stride + p.gate_off + head]));
+    }
+    T* og = reinterpret_cast<T*>(p.out) + (size_t)tok * p.out_stride + p.out_off + (size_t)head * d;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+        const int e = lane + 32 * i;
+        if (e < d) og[e] = from_f32<T>(o[i] * f);
+    }
+}
+
+MSGL_API int msgl_window_attention(const void* q, const void* k_cache, const void* v_cache, const int* q_start, const int* kv_len,
+                                   const int* block_table, int bt_stride, int uniform, int n_tiles,
+                                   const float* bias, int bias_len, const void* gate, long long gate_stride, int gate_off,
+                                   void* out, long long out_stride, int out_off, int B, int n_q, int n_kv, int d, int page_size,
+                                   int window, int keep_first, int QT, int GH, float scale, float out_scale, int dtype,
+                                   cudaStream_t stream) {
+    if (n_tiles <= 0) return MSGL_OK;
+    if (d <= 0 || d > 32 * WA_MAX_DPL || n_kv <= 0 || n_q % n_kv || QT < 1 || GH < 1 || QT * GH > WA_ROWS || page_size < 1)
+        return MSGL_ERR_SIZE;
+    WindowAttnParams p;
+    p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.q_start = q_start; p.kv_len = kv_len; p.block_table = block_table;
+    p.bt_stride = bt_stride; p.uniform = uniform; p.bias = bias; p.bias_len = bias_len; p.gate = gate;
+    p.gate_stride = gate_stride; p.gate_off = gate_off; p.out = out; p.out_stride = out_stride; p.out_off = out_off; p.B = B;
+    p.n_q = n_q; p.n_kv = n_kv; p.d = d; p.page_size = page_size; p.window = window; p.keep_first = keep_first; p.QT = QT;
+    p.GH = GH; p.scale = scale; p.out_scale = out_scale;
+    const int G = n_q / n_kv;
+    const dim3 grid(n_tiles, n_kv * ((G + GH - 1) / GH));
+    const size_t smem = ((size_t)WA_ROWS * d + (size_t)WA_KC * (d + 1) + (size_t)WA_KC * d) * sizeof(float);
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    const int dpl = (d + 31) / 32;
+#define WA_LAUNCH(N)                                                                                                        \
+    do {                                                                                                                    \
+        static MsglOncePerDevice once;                                                                                      \
+        if (smem > 48 * 1024 && once.due()) {                                                                               \
+            cudaFuncSetAttribute(window_attention_kernel<float, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            cudaFuncSetAttribute(window_attention_kernel<__nv_bfloat16, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            once.mark();                                                                                                    \
+        }                                                                                                                   \
+        if (dtype == MSGL_F32) window_attention_kernel<float, N><<<grid, WA_ROWS * 32, smem, stream>>>(p);                  \
+        else window_attention_kernel<__nv_bfloat16, N><<<grid, WA_ROWS * 32, smem, stream>>>(p);                            \
+    } while (0)
+    if (dpl <= 1) WA_LAUNCH(1);
+    else if (dpl <= 2) WA_LAUNCH(2);
+    else if (dpl <= 3) WA_LAUNCH(3);
+    else if (dpl <= 4) WA_LAUNCH(4);
+    else if (dpl <= 8) WA_LAUNCH(8);
+    else WA_LAUNCH(16);
+#undef WA_LAUNCH
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// Linear attention with a fixed decay per head
+//
+//   q = silu(proj q), k = silu(proj k) [heads][dk], v = silu(proj v) [heads][dv]
+//   S_t = decay_h * S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t;  S per request [slot][heads][dk][dv] float32
+//
+// A block owns 32 columns of one (request, head) state and walks the request's tokens of the step in order; the
+// column's dk rows are dealt out to 8 neighbouring lanes, which add their parts of o with shuffles.
+// ---------------------------------------------------------------------------------------
+#define DA_COLS 32
+#define DA_PARTS 8
+#define DA_MAX_ROWS 64      // most rows of a column per lane: key sizes up to 512
+
+template <typename T, int NR /* rows of a column per lane: key sizes up to DA_PARTS * NR */>
+__global__ void __launch_bounds__(DA_COLS * DA_PARTS)
+decay_attention_kernel(const void* proj_, long long stride, int q_off, int k_off, int v_off, int heads, int dk, int dv,
+                       const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ q_start,
+                       const int* __restrict__ slots, float* __restrict__ out /* [T, heads * dv] */) {
+    extern __shared__ float qk[];                    // [2][2][dk]: double-buffered q and k of the current token
+    const int r = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DA_COLS;
+    const int tid = threadIdx.x;
+    const int part = tid & (DA_PARTS - 1), col = col0 + (tid >> 3);
+    const bool col_ok = col < dv;
+    const int t0 = q_start[r], n = q_start[r + 1] - t0;
+    const int slot = slots[r];
+    const float a = decay[h];
+    const T* proj = reinterpret_cast<const T*>(proj_);
+    float* S = state + (((size_t)slot * heads + h) * dk) * dv;
+    const int rows = (dk + DA_PARTS - 1) / DA_PARTS;             // rows i = part + DA_PARTS * j
+    float s[NR];
+#pragma unroll
+    for (int j = 0; j < NR; ++j) {
+        const int i = part + DA_PARTS * j;
+        s[j] = (j < rows && i < dk && col_ok) ? S[(size_t)i * dv + col] : 0.f;
+    }
+    for (int tt = 0; tt < n; ++tt) {
+        const size_t row = (size_t)(t0 + tt) * stride;
+        float* qb = qk + (tt & 1) * 2 * dk;
+        float* kb = qb + dk;
+        for (int i = tid; i < 2 * dk; i += DA_COLS * DA_PARTS) {
+            const int c = i < dk ? q_off + h * dk + i : k_off + h * dk + (i - dk);
+            qb[i] = siluf_(to_f32<T>(proj[row + c]));
+        }
+        const float v = col_ok ? siluf_(to_f32<T>(proj[row + v_off + h * dv + col])) : 0.f;
+        __syncthreads();
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < NR; ++j) {
+            if (j < rows) {
+                const int i = part + DA_PARTS * j;
+                if (i < dk) {
+                    s[j] = fmaf(a, s[j], kb[i] * v);
+                    acc = fmaf(s[j], qb[i], acc);
+                }
+            }
+        }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+        if (part == 0 && col_ok) out[(size_t)(t0 + tt) * heads * dv + h * dv + col] = acc;
+    }
+#pragma unroll
+    for (int j = 0; j < NR; ++j) {
+        const int i = part + DA_PARTS * j;
+        if (j < rows && i < dk && col_ok) S[(size_t)i * dv + col] = s[j];
+    }
+}
+
+MSGL_API int msgl_decay_attention(const void* proj, long long stride, int q_off, int k_off, int v_off, int heads, int dk, int dv,
+                                  const float* decay, float* state, const int* q_start, const int* slots, float* out, int B,
+                                  int dtype, cudaStream_t stream) {
+    if (B <= 0) return MSGL_OK;
+    if (heads <= 0 || dk <= 0 || dv <= 0 || dk > DA_PARTS * DA_MAX_ROWS) return MSGL_ERR_SIZE;
+    const dim3 grid(B, heads, (dv + DA_COLS - 1) / DA_COLS);
+    const size_t smem = (size_t)4 * dk * sizeof(float);
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    const int nr = (dk + DA_PARTS - 1) / DA_PARTS;
+#define DA_LAUNCH(N)                                                                                                                 \
+    do {                                                                                                                             \
+        if (dtype == MSGL_F32)                                                                                                       \
+            decay_attention_kernel<float, N><<<grid, DA_COLS * DA_PARTS, smem, stream>>>(proj, stride, q_off, k_off, v_off, heads, dk, \
+                                                                                         dv, decay, state, q_start, slots, out);   \
+        else                                                                                                                         \
+            decay_attention_kernel<__nv_bfloat16, N><<<grid, DA_COLS * DA_PARTS, smem, stream>>>(proj, stride, q_off, k_off, v_off,    \
+                                                                                                 heads, dk, dv, decay, state,      \
+                                                                                                 q_start, slots, out);             \
+    } while (0)
+    if (nr <= 4) DA_LAUNCH(4);
+    else if (nr <= 8) DA_LAUNCH(8);
+    else if (nr <= 16) DA_LAUNCH(16);
+    else if (nr <= 32) DA_LAUNCH(32);
+    else DA_LAUNCH(64);
+#undef DA_LAUNCH
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// y = x / sqrt(mean(x^2) + eps) * w * sigmoid(gate) * c   (x float32 [T, N]; gate and y in packed rows)
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rms_gate_kernel(const float* __restrict__ x, int N, const float* __restrict__ w, float eps, const void* gate_,
+                                long long gate_stride, int gate_off, void* out_, long long out_stride, int out_off, float c) {
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const float* xr = x + (size_t)t * N;
+    float ssq = 0.f;
+    for (int i = threadIdx.x; i < N; i += blockDim.x) ssq += xr[i] * xr[i];
+    ssq = block_sum(ssq, red);
+    const float rs = 1.f / sqrtf(ssq / (float)N + eps);
+    const T* g = gate_ ? reinterpret_cast<const T*>(gate_) + (size_t)t * gate_stride + gate_off : nullptr;
+    T* o = reinterpret_cast<T*>(out_) + (size_t)t * out_stride + out_off;
+    for (int i = threadIdx.x; i < N; i += blockDim.x) {
+        float y = xr[i] * rs * w[i];
+        if (g) y *= sigmoidf_(to_f32<T>(g[i]));
+        o[i] = from_f32<T>(y * c);
+    }
+}
+
+MSGL_API int msgl_rms_gate(const float* x, int N, const float* w, float eps, const void* gate, long long gate_stride, int gate_off,
+                           void* out, long long out_stride, int out_off, float c, int T, int dtype, cudaStream_t stream) {
+    if (T <= 0) return MSGL_OK;
+    if (N <= 0) return MSGL_ERR_SIZE;
+    const int threads = N >= 1024 ? 256 : 128;
+    if (dtype == MSGL_F32)
+        rms_gate_kernel<float><<<T, threads, 0, stream>>>(x, N, w, eps, gate, gate_stride, gate_off, out, out_stride, out_off, c);
+    else if (dtype == MSGL_BF16)
+        rms_gate_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(x, N, w, eps, gate, gate_stride, gate_off, out, out_stride, out_off, c);
+    else
+        return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// out = act(gate) * up; act 0 = silu, 1 = gelu (tanh form)
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gated_act_kernel(const void* in_, long long in_stride, int gate_off, int up_off, void* out_, long long out_stride,
+                                 int out_off, int I, int act, long long total) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const long long t = idx / I;
+    const int i = (int)(idx - t * I);
+    const T* in = reinterpret_cast<const T*>(in_) + t * in_stride;
+    const float g = to_f32<T>(in[gate_off + i]), u = to_f32<T>(in[up_off + i]);
+    const float a = act == 1 ? gelu_tanhf_(g) : siluf_(g);
+    reinterpret_cast<T*>(out_)[t * out_stride + out_off + i] = from_f32<T>(a * u);
+}
+
+MSGL_API int msgl_gated_act(const void* in, long long in_stride, int gate_off, int up_off, void* out, long long out_stride,
+                            int out_off, int I, int act, int T, int dtype, cudaStream_t stream) {
+    if (T <= 0 || I <= 0) return MSGL_OK;
+    if (act != 0 && act != 1) return MSGL_ERR_SIZE;
+    const long long total = (long long)T * I;
+    const int blocks = (int)((total + 255) / 256);
+    if (dtype == MSGL_F32)
+        gated_act_kernel<float><<<blocks, 256, 0, stream>>>(in, in_stride, gate_off, up_off, out, out_stride, out_off, I, act, total);
+    else if (dtype == MSGL_BF16)
+        gated_act_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(in, in_stride, gate_off, up_off, out, out_stride, out_off, I, act, total);
+    else
+        return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}

@@ -11,8 +11,9 @@ manager and kernels that generation uses; nothing is sampled).  For a step in wh
 wanted, `<out>/<step>.f32` holds them as little-endian float32 [wanted, vocab], in the order of
 the entries and of `want`.  After every step a line `done <step>` is printed and flushed.
 Requests named in `end` give back what they hold after the step.  The cache pool is sized for
-`--max-tokens` tokens held by live requests, each request rounded up to a multiple of 64, so
-pages are used again.
+`--max-tokens` tokens held by live requests, each request rounded up to a multiple of 64, and
+there are `--max-requests` request slots (rows of the block tables and of the per-request
+states), so pages and slots are used again.
 """
 
 from __future__ import annotations
@@ -32,7 +33,7 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True)
     ap.add_argument("--max-tokens", type=int, required=True)
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page; must divide 64")
-    ap.add_argument("--max-requests", type=int, default=8, help="request slots (live requests at a time)")
+    ap.add_argument("--max-requests", type=int, default=4, help="request slots (live requests at a time)")
     ap.add_argument("--no-cuda-graph", action="store_true")
     args = ap.parse_args(argv)
     if args.page_size < 1 or 64 % args.page_size:
@@ -45,7 +46,8 @@ def main(argv=None) -> int:
 
     num_pages = max(-(-args.max_tokens // 64) * 64 // args.page_size, 1)
     runner = ModelRunner.from_model_dir(args.model, dtype=args.dtype, page_size=args.page_size, num_pages=num_pages,
-                                        max_reqs=args.max_requests, use_cuda_graph=not args.no_cuda_graph)
+                                        max_reqs=args.max_requests, max_context_len=num_pages * args.page_size,
+                                        use_cuda_graph=not args.no_cuda_graph)
     slots = {}
     for line in sys.stdin:
         line = line.strip()

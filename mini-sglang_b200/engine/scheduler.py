@@ -211,7 +211,8 @@ class Scheduler:
         w = self.mgr.groups[gi].window
         if w is None:
             return n_tokens
-        return min(n_tokens, w + portion + self.P)
+        kept = self.mgr.groups[gi].keep_pages * self.P      # the first tokens' pages, which the window never gives back
+        return min(n_tokens, w + portion + self.P + kept)
 
     def _portion(self, n_unfed: int) -> int:
         return max(1, min(n_unfed, self.chunk_size, self.max_step_tokens))

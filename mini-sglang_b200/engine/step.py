@@ -277,7 +277,8 @@ class ModelRunner:
         self.max_step_tokens = max_step_tokens
         env = BuildEnv(dtype=self.dtype, device=self.device)
         self.model = DecoderModel(spec, env)
-        head_dims = sorted({n.head_dim for n in self.model.cache_needs().values() if isinstance(n, PagedKVNeed)})
+        head_dims = sorted({n.head_dim for n in self.model.cache_needs().values()
+                            if isinstance(n, PagedKVNeed) and n.library == "attention"})
         ops.warm_up(head_dims)
         expected = self.model.tensors()
         src = source_factory(expected, self.dtype, self.device)
@@ -326,13 +327,17 @@ class ModelRunner:
             cid = g.cache_ids[0]
             need = needs[cid]
             G = max(need.q_heads // need.n_kv_heads, 1) if need.q_heads else 1
+            if need.library != "attention":
+                # a mixer with attention kernels of its own: its launches take every request whole (no kv splits)
+                self._group_geom.append((need.n_kv_heads, G, 0, 0))
+                continue
             qt = ops.attention_tile_tokens(ops.VARIANT_MMA_DECODE, G, need.head_dim) if ops.mma_supported(need.head_dim, self.dtype) \
                 else ops.attention_tile_tokens(ops.VARIANT_SIMT, G)
             self._group_geom.append((need.n_kv_heads, G, ops.decode_blocks_per_sm(need.head_dim, self.dtype, G), qt))
         # blocks per kv head of a decode launch with an even cut of the keys: what the SMs hold at once; empty unless the
         # decode kernel of every group takes such a cut
         self._even_nb: List[int] = []
-        if self.dtype == torch.bfloat16 and self.mgr.groups:
+        if self.dtype == torch.bfloat16 and self.mgr.groups and all(geom[2] for geom in self._group_geom):
             ok = True
             for g, (n_kv, G, per_sm, _) in zip(self.mgr.groups, self._group_geom):
                 head_dim = needs[g.cache_ids[0]].head_dim
@@ -399,6 +404,8 @@ class ModelRunner:
     def _plan_splits(self, gi: int, q_lens: Sequence[int], kv_lens: Sequence[int], cap: int,
                      long_cap: Optional[int] = None, fused_blocks: int = 0) -> List[int]:
         n_kv, G, per_sm, qt = self._group_geom[gi]
+        if not per_sm:
+            return [1] * len(q_lens)
         warps = DECODE_WARPS
         if fused_blocks:          # the whole-step kernel: its blocks are the places, a unit is a (request, kv head, split)
             per_sm, warps, qt = max(fused_blocks // self.sm_count, 1), self.FUSED_WARPS, 1
@@ -493,6 +500,9 @@ class ModelRunner:
             views[cid] = KVCacheView(k, v, ctx.groups[self.mgr.group_of_cache[cid]], self.page_size)
         for cid, st in self.storage.state.items():
             views[cid] = StateCacheView(st)
+        # the caches of a mixer with several needs, (c, 0), (c, 1), ..., reach it as one tuple under the run's id c
+        for c in sorted({cid[0] for cid in views if isinstance(cid, tuple)}):
+            views[c] = tuple(views[cid] for cid in sorted(k for k in views if isinstance(k, tuple) and k[0] == c))
         return views
 
     # -- the step ----------------------------------------------------------------------------
@@ -599,6 +609,8 @@ class ModelRunner:
 
     def _graph_max_split(self, gi: int, b: int) -> int:
         n_kv, G, per_sm, _ = self._group_geom[gi]
+        if not per_sm:
+            return 1
         chunks = 1 if G <= 16 else -(-G // 16)
         blocks = b * n_kv * chunks
         places = self._fused_blocks(b) or self.sm_count * per_sm

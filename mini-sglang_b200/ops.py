@@ -622,6 +622,184 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
 
 
 # ---------------------------------------------------------------------------------------
+# norms, convolutions, windowed and linear attention, gated activations (csrc/mixers.cu)
+# ---------------------------------------------------------------------------------------
+_mixers = None
+ACT_SILU, ACT_GELU_TANH = 0, 1
+WINDOW_ATTENTION_ROWS = 8         # (token, head) rows of a block of the windowed attention kernel
+CONV_MAX_TAPS = 16
+WINDOW_ATTENTION_MAX_HEAD_DIM = 512
+DECAY_ATTENTION_MAX_KEY_DIM = 512
+
+
+def _mix_lib():
+    global _mixers
+    if _mixers is None:
+        lib = _build.mixers_library()
+        lib.msgl_dyntanh.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
+                                     c_int, c_void_p]
+        lib.msgl_conv_norm_kvwrite.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_int] + [c_void_p] * 4 + \
+            [c_float] + [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_void_p]
+        lib.msgl_window_attention.argtypes = [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_ll, c_int,
+                                              c_void_p, c_ll, c_int] + [c_int] * 9 + [c_float, c_float, c_int, c_void_p]
+        lib.msgl_decay_attention.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int] + [c_void_p] * 5 + \
+            [c_int, c_int, c_void_p]
+        lib.msgl_rms_gate.argtypes = [c_void_p, c_int, c_void_p, c_float, c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_float, c_int,
+                                      c_int, c_void_p]
+        lib.msgl_gated_act.argtypes = [c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        _mixers = lib
+    return _mixers
+
+
+def _rows_view(t: torch.Tensor, width: int, what: str) -> int:
+    """A [T, width] view into packed rows: unit stride along the row; -> the row stride in elements."""
+    assert t.dim() == 2 and t.shape[1] == width and (t.stride(1) == 1 or width == 1), f"{what}: [T, {width}] with unit stride wanted"
+    return t.stride(0)
+
+
+def dyntanh(weight: torch.Tensor, bias: torch.Tensor, alpha: float, *, x: Optional[torch.Tensor] = None,
+            residual: Optional[torch.Tensor] = None, residual_out: Optional[torch.Tensor] = None,
+            rows: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """y = tanh(alpha * v) * weight + bias with v = residual + x in float32 (either may be None); v goes to `residual_out`
+    when it is given; `rows` (int32) picks the rows.  x: float32 or `out_dtype`; weight, bias: float32 [H]."""
+    _need_cuda(weight, bias, x, residual, residual_out, rows)
+    src = x if x is not None else residual
+    assert src is not None and src.dim() == 2 and src.is_contiguous()
+    H = src.shape[1]
+    assert weight.dtype == torch.float32 and bias.dtype == torch.float32 and weight.numel() == H and bias.numel() == H
+    if x is not None:
+        assert x.dtype in (torch.float32, out_dtype) and x.is_contiguous()
+    if residual is not None:
+        assert residual.dtype == torch.float32 and residual.shape[1] == H and residual.is_contiguous()
+    n_out = rows.numel() if rows is not None else src.shape[0]
+    out = torch.empty((n_out, H), dtype=out_dtype, device=src.device)
+    code = _mix_lib().msgl_dyntanh(_ptr(x), int(x is not None and x.dtype == torch.float32), _ptr(residual), _ptr(residual_out),
+                                   _ptr(rows), _ptr(weight), _ptr(bias), float(alpha), _ptr(out), n_out, H, _DT[out_dtype], _stream())
+    _check(code, "dyntanh")
+    return out
+
+
+def conv_norm_kvwrite(q_in: torch.Tensor, k_in: torch.Tensor, *, n_kv: int, head_dim: int, q_taps: torch.Tensor, k_taps: torch.Tensor,
+                      q_norm: torch.Tensor, k_norm: torch.Tensor, eps: float, state: torch.Tensor, token_req: torch.Tensor,
+                      q_start: torch.Tensor, slots: torch.Tensor, out_loc: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                      v_cache: Optional[torch.Tensor], page_size: int) -> torch.Tensor:
+    """Short causal convolution over time on every channel of q_in [T, Cq] and k_in [T, Ck] (views into one packed
+    projection), continued from `state` [slots, taps - 1, Cq + Ck] (the request's last inputs, which the call brings up to
+    date), then an RMS norm over the whole of q and of k.  The normed k goes to `k_cache`, the un-normed k to `v_cache`
+    (layout [page][kv head][slot][head_dim]) at token slots `out_loc`; the normed q comes back as [T, Cq]."""
+    _need_cuda(q_in, k_in, q_taps, k_taps, q_norm, k_norm, state, token_req, q_start, slots, out_loc, k_cache, v_cache)
+    T, Cq, Ck = q_in.shape[0], q_in.shape[1], k_in.shape[1]
+    stride = _rows_view(q_in, Cq, "q")
+    assert _rows_view(k_in, Ck, "k") == stride and q_in.dtype == k_in.dtype
+    item = q_in.element_size()
+    q_off = 0
+    k_off = (k_in.data_ptr() - q_in.data_ptr()) // item
+    taps = q_taps.shape[1]
+    assert q_taps.shape == (Cq, taps) and k_taps.shape == (Ck, taps) and q_taps.dtype == torch.float32 and k_taps.dtype == torch.float32
+    assert q_taps.is_contiguous() and k_taps.is_contiguous()
+    assert q_norm.dtype == torch.float32 and k_norm.dtype == torch.float32 and q_norm.numel() == Cq and k_norm.numel() == Ck
+    assert state.dtype == q_in.dtype and state.is_contiguous() and tuple(state.shape[1:]) == (max(taps - 1, 0), Cq + Ck)
+    if k_cache is not None:
+        assert k_cache.dtype == q_in.dtype and v_cache.dtype == q_in.dtype and out_loc is not None and out_loc.numel() == T
+    q_out = torch.empty((T, Cq), dtype=q_in.dtype, device=q_in.device)
+    B = q_start.numel() - 1
+    code = _mix_lib().msgl_conv_norm_kvwrite(_ptr(q_in), stride, q_off, k_off, Cq, Ck, head_dim, n_kv, taps, _ptr(q_taps), _ptr(k_taps),
+                                             _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(state), _ptr(token_req), _ptr(q_start),
+                                             _ptr(slots), _ptr(out_loc), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), page_size, T, B,
+                                             _dt(q_in), _stream())
+    _check(code, f"conv_norm_kvwrite ({taps} taps)")
+    global LAUNCHES
+    LAUNCHES += int(taps > 1)
+    return q_out
+
+
+def window_attention_geometry(n_q: int, n_kv: int) -> Tuple[int, int]:
+    """(tokens per query tile, query heads of one kv head per block) of the windowed attention kernel."""
+    G = n_q // n_kv
+    gh = min(G, WINDOW_ATTENTION_ROWS)
+    return WINDOW_ATTENTION_ROWS // gh, gh
+
+
+def window_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *, q_start: torch.Tensor,
+                     kv_len: torch.Tensor, block_table: torch.Tensor, n_kv: int, page_size: int, window: int, keep_first: int,
+                     scale: float, q_lens: Optional[Sequence[int]], bias: Optional[torch.Tensor] = None,
+                     gate: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> None:
+    """Causal softmax attention over the paged cache in which the query at position i sees key j if i - j < window or
+    j < keep_first (window <= 0: every earlier key).  bias: float32 [heads, L], added to the scaled score by distance
+    min(i - j, L - 1).  gate: [T, heads] (a view into packed rows): the head's output is multiplied by its sigmoid; out_scale
+    multiplies everything.  q [T, heads, d]; out [T, heads * d] (may be a view into packed rows).  q_lens: the requests'
+    numbers of tokens as the host knows them (they size the launch), or None when every request brings one token."""
+    _need_cuda(q, out, k_cache, v_cache, q_start, kv_len, block_table, bias, gate)
+    T, n_q, d = q.shape
+    assert q.is_contiguous() and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype and out.dtype == q.dtype
+    out_stride = _rows_view(out, n_q * d, "out")
+    B = kv_len.numel()
+    QT, GH = window_attention_geometry(n_q, n_kv)
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.dim() == 2 and bias.shape[0] == n_q and bias.is_contiguous()
+    gate_stride = 0
+    if gate is not None:
+        assert gate.dtype == q.dtype
+        gate_stride = _rows_view(gate, n_q, "gate")
+    n_tiles = sum(-(-n // QT) for n in q_lens) if q_lens is not None else B
+    code = _mix_lib().msgl_window_attention(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0),
+        int(q_lens is None), n_tiles,
+        _ptr(bias), bias.shape[1] if bias is not None else 0, _ptr(gate), gate_stride, 0, _ptr(out), out_stride, 0,
+        B, n_q, n_kv, d, page_size, int(window), int(keep_first), QT, GH, float(scale), float(out_scale), _dt(q), _stream())
+    _check(code, f"window_attention (head size {d})")
+
+
+def decay_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, heads: int, decay: torch.Tensor, state: torch.Tensor,
+                    q_start: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """Linear attention with a fixed decay per head over the step's tokens, continued from and written back to `state`
+    [slots, heads, dk, dv] float32: S <- decay_h S + k v^T, o = S^T q with q, k, v = silu of the given projections
+    ([T, heads * dk], [T, heads * dk], [T, heads * dv]: views into one packed projection).  -> float32 [T, heads * dv]."""
+    _need_cuda(q, k, v, decay, state, q_start, slots)
+    T = q.shape[0]
+    dk, dv = q.shape[1] // heads, v.shape[1] // heads
+    stride = _rows_view(q, heads * dk, "q")
+    assert _rows_view(k, heads * dk, "k") == stride and _rows_view(v, heads * dv, "v") == stride and q.dtype == k.dtype == v.dtype
+    item = q.element_size()
+    k_off, v_off = (k.data_ptr() - q.data_ptr()) // item, (v.data_ptr() - q.data_ptr()) // item
+    assert decay.dtype == torch.float32 and decay.numel() == heads
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dk, dv)
+    out = torch.empty((T, heads * dv), dtype=torch.float32, device=q.device)
+    B = q_start.numel() - 1
+    code = _mix_lib().msgl_decay_attention(_ptr(q), stride, 0, k_off, v_off, heads, dk, dv, _ptr(decay), _ptr(state), _ptr(q_start),
+                                           _ptr(slots), _ptr(out), B, _dt(q), _stream())
+    _check(code, f"decay_attention (key size {dk})")
+    return out
+
+
+def rms_gate(x: torch.Tensor, weight: torch.Tensor, eps: float, gate: Optional[torch.Tensor], out: torch.Tensor, scale: float = 1.0) -> None:
+    """out = x / sqrt(mean(x^2) + eps) * weight * sigmoid(gate) * scale; x float32 [T, N] contiguous, weight float32 [N],
+    gate and out [T, N] views into packed rows of the activation type."""
+    _need_cuda(x, weight, gate, out)
+    T, N = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and weight.dtype == torch.float32 and weight.numel() == N
+    gs = _rows_view(gate, N, "gate") if gate is not None else 0
+    if gate is not None:
+        assert gate.dtype == out.dtype
+    code = _mix_lib().msgl_rms_gate(_ptr(x), N, _ptr(weight), float(eps), _ptr(gate), gs, 0, _ptr(out), _rows_view(out, N, "out"), 0,
+                                    float(scale), T, _dt(out), _stream())
+    _check(code, "rms_gate")
+
+
+def gated_act(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, act: int) -> None:
+    """out = act(gate) * up, act = ACT_SILU or ACT_GELU_TANH (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))); all three
+    [T, I] views into packed rows."""
+    _need_cuda(gate, up, out)
+    T, I = gate.shape
+    stride = _rows_view(gate, I, "gate")
+    assert _rows_view(up, I, "up") == stride and gate.dtype == up.dtype == out.dtype
+    up_off = (up.data_ptr() - gate.data_ptr()) // gate.element_size()
+    code = _mix_lib().msgl_gated_act(_ptr(gate), stride, 0, up_off, _ptr(out), _rows_view(out, I, "out"), 0, I, int(act), T, _dt(gate),
+                                     _stream())
+    _check(code, "gated_act")
+
+
+# ---------------------------------------------------------------------------------------
 # the whole decode step in one persistent kernel (csrc/decode_step.cu)
 # ---------------------------------------------------------------------------------------
 # Off unless MSGL_FUSED_DECODE=1: measured on B200 at Qwen3-8B's sizes the one-kernel step takes 4.2 / 5.4 ms at batch 1 / 8

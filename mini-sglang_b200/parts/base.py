@@ -75,6 +75,35 @@ class Mixer(Part):
         raise NotImplementedError
 
 
+class Projected:
+    """A part that reads its input only through matrix products and ends in one:
+
+        forward(x) = out_weight() @ middle(in_weight() @ x)
+
+    `in_weight()` [in_width, H] stacks the part's input projections row-wise and `out_weight()` [H, mid_width] is its output
+    projection; `middle(proj [T, in_width], act [T, mid_width], ctx, cache, writes_cache, out_scale)` computes everything
+    between them, reading views into packed rows and writing its result, times `out_scale`, into `act`.  A block arrangement
+    whose sublayers read the same input can then stack the input projections of all of them into one product and their output
+    projections into another (ParallelSharedNormBlock); `forward` of such a part runs the same three steps alone."""
+
+    def in_weight(self) -> torch.Tensor:
+        raise NotImplementedError
+
+    def out_weight(self) -> torch.Tensor:
+        raise NotImplementedError
+
+    def middle(self, proj, act, ctx, cache=None, writes_cache: bool = True, out_scale: float = 1.0) -> None:
+        raise NotImplementedError
+
+    def forward_projected(self, x, ctx, cache=None, writes_cache: bool = True):
+        from .. import ops
+        proj = ops.linear(x, self.in_weight())
+        w_out = self.out_weight()
+        act = torch.empty((x.shape[0], w_out.shape[1]), dtype=x.dtype, device=x.device)
+        self.middle(proj, act, ctx, cache, writes_cache)
+        return ops.linear(act, w_out)
+
+
 class FeedForward(Part):
     # False if forward() reads device data on the host or launches work whose shapes depend on the
     # tokens (routing by gathered rows, say): a decode step with such a part is not captured in a CUDA graph.

@@ -3,7 +3,10 @@ from __future__ import annotations
 from typing import Dict
 
 from ..weights.loader import TensorDecl
-from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Block, BuildEnv, build_part,
+import torch
+
+from .. import ops
+from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Block, BuildEnv, Projected, build_part,
                    register_block)
 
 
@@ -57,3 +60,72 @@ class PreNormResidualBlock(Block):
         if any(v is None for v in parts.values()):
             return None
         return {"kind": "prenorm_residual", **parts}
+
+
+@register_block("parallel_shared_norm")
+class ParallelSharedNormBlock(Block):
+    """res += delta_in; y = norm(res); delta_out = mixer(y) + ffn(y): one norm, whose output the mixer and the feed-forward
+    read side by side; the layer may have no feed-forward.  The sum comes back un-added in float32, so that the next norm
+    fuses it into the float32 stream.
+
+    Where the mixer and the feed-forward are given by their projections (`Projected`), the layer is two matrix products:
+    every input projection of both stacked row-wise into one, every output projection stacked along its inner dimension into
+    the other, whose float32 result is the sum of the sublayers.  The stacked matrices are padded with zeros to the row
+    and inner sizes that the weight-streaming kernel for a few tokens takes.  Role of the norm: "input"."""
+
+    ROWS_TO, INNER_TO = 16, 32
+
+    def __init__(self, layer_spec, env: BuildEnv):
+        super().__init__(None, layer_spec.prefix, env)
+        at = layer_spec.part_prefix
+        self.norm_in = build_part(NORMS, "norm", layer_spec.norms["input"], at("input"), env)
+        self.mixer = build_part(MIXERS, "mixer", layer_spec.mixer, at("mixer"), env, position=None)
+        self.ffn = None
+        if layer_spec.feed_forward is not None:
+            self.ffn = build_part(FEED_FORWARDS, "feed-forward", layer_spec.feed_forward, at("feed_forward"), env)
+        self.stacked = isinstance(self.mixer, Projected) and (self.ffn is None or isinstance(self.ffn, Projected))
+        self.w_in = self.w_out = None
+
+    def parts(self):
+        return [p for p in (self.norm_in, self.mixer, self.ffn) if p is not None]
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        out: Dict[str, TensorDecl] = {}
+        for part in self.parts():
+            out.update(part.tensors())
+        return out
+
+    def load(self, src) -> None:
+        for part in self.parts():
+            part.load(src)
+        if not self.stacked:
+            return
+        subs = [p for p in (self.mixer, self.ffn) if p is not None]
+        self.in_widths = [p.in_weight().shape[0] for p in subs]
+        self.mid_widths = [p.out_weight().shape[1] for p in subs]
+        w_in = torch.cat([p.in_weight() for p in subs], dim=0)
+        w_out = torch.cat([p.out_weight() for p in subs], dim=1)
+        pad_rows = -w_in.shape[0] % self.ROWS_TO
+        pad_inner = -w_out.shape[1] % self.INNER_TO
+        if pad_rows:
+            w_in = torch.cat((w_in, w_in.new_zeros((pad_rows, w_in.shape[1]))), dim=0)
+        if pad_inner:
+            w_out = torch.cat((w_out, w_out.new_zeros((w_out.shape[0], pad_inner))), dim=1)
+        self.w_in, self.w_out, self.pad_inner = w_in.contiguous(), w_out.contiguous(), pad_inner
+
+    def forward(self, delta, residual, ctx, cache, writes_cache: bool = True):
+        y = self.norm_in.forward(x=delta, residual=residual, residual_out=residual if delta is not None else None)
+        if not self.stacked:
+            out = self.mixer.forward(y, ctx, cache, writes_cache).float()
+            if self.ffn is not None:
+                out = out + self.ffn.forward(y, ctx).float()
+            return out, residual
+        proj = ops.linear(y, self.w_in)
+        act = torch.empty((y.shape[0], self.w_out.shape[1]), dtype=y.dtype, device=y.device)
+        if self.pad_inner:
+            act[:, act.shape[1] - self.pad_inner:].zero_()
+        a, m = self.in_widths[0], self.mid_widths[0]
+        self.mixer.middle(proj[:, :a], act[:, :m], ctx, cache, writes_cache)
+        if self.ffn is not None:
+            self.ffn.middle(proj[:, a:a + self.in_widths[1]], act[:, m:m + self.mid_widths[1]], ctx)
+        return ops.linear(act, self.w_out, out_dtype=torch.float32), residual

@@ -6,7 +6,7 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorDecl
-from .base import FeedForward, register_feed_forward
+from .base import FeedForward, Projected, register_feed_forward
 
 
 @register_feed_forward("swiglu_mlp")
@@ -36,3 +36,46 @@ class SwiGLUMLP(FeedForward):
 
     def fused_decode_fields(self):
         return {"kind": "swiglu_mlp", "gate_up": self.gate_up, "down": self.down, "H": self.H, "I": self.I}
+
+
+ACTIVATIONS = {"silu": ops.ACT_SILU, "gelu_tanh": ops.ACT_GELU_TANH}
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP(FeedForward, Projected):
+    """down(act(gate(x)) * up(x)), dense, no biases, with act = "silu" or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z +
+    0.044715 z^3)))).  gate and up are packed row-wise into one [2I, H] matrix.  params: hidden_size, intermediate_size,
+    activation, names (what the checkpoint calls gate, up and down below the part's prefix; default "gate_proj.weight" ...)."""
+
+    def __init__(self, spec, prefix, env):
+        super().__init__(spec, prefix, env)
+        self.H, self.I = int(spec["hidden_size"]), int(spec["intermediate_size"])
+        act = spec.get("activation", "silu")
+        if act not in ACTIVATIONS:
+            raise ValueError(f"unknown activation {act!r}; known: " + ", ".join(sorted(ACTIVATIONS)))
+        self.act = ACTIVATIONS[act]
+        names = spec.get("names") or {}
+        self.n_gate, self.n_up, self.n_down = (self.name(names.get(k, d)) for k, d in
+                                                (("gate", "gate_proj.weight"), ("up", "up_proj.weight"), ("down", "down_proj.weight")))
+        self.gate_up = self.down = None
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        return {self.n_gate: TensorDecl((self.I, self.H)), self.n_up: TensorDecl((self.I, self.H)),
+                self.n_down: TensorDecl((self.H, self.I))}
+
+    def load(self, src) -> None:
+        self.gate_up = torch.cat((src.fetch(self.n_gate), src.fetch(self.n_up)), dim=0).contiguous()
+        self.down = src.fetch(self.n_down).contiguous()
+
+    def in_weight(self):
+        return self.gate_up
+
+    def out_weight(self):
+        return self.down
+
+    def middle(self, proj, act, ctx, cache=None, writes_cache=True, out_scale=1.0):
+        assert out_scale == 1.0
+        ops.gated_act(proj[:, :self.I], proj[:, self.I:2 * self.I], act, self.act)
+
+    def forward(self, x, ctx):
+        return self.forward_projected(x, ctx)

@@ -55,17 +55,20 @@ class DecoderModel:
         self.fused_decode = FusedDecodeStep.build(self)      # None: this model is stepped kernel by kernel
 
     def cache_needs(self) -> Dict[int, object]:
-        """cache id -> need, from the mixer of the run that writes the cache."""
-        needs: Dict[int, object] = {}
+        """cache id -> need, from the mixer of the run that writes the cache.  A mixer that declares a tuple of needs
+        gets the caches (id, 0), (id, 1), ...; its forward then receives the tuple of their views."""
+        needs: Dict[object, object] = {}
         for run in self.schedule:
             if run.cache is None or not run.writes_cache:
                 continue
             need = self.layers[run.layer].mixer.cache_need()
             if need is None:
                 continue
-            if run.cache in needs and needs[run.cache] != need:
-                raise ValueError(f"cache {run.cache} is written by mixers with different needs")
-            needs[run.cache] = need
+            several = {(run.cache, k): n for k, n in enumerate(need)} if isinstance(need, tuple) else {run.cache: need}
+            for cid, n in several.items():
+                if cid in needs and needs[cid] != n:
+                    raise ValueError(f"cache {run.cache} is written by mixers with different needs")
+                needs[cid] = n
         return needs
 
     # -- compute -----------------------------------------------------------------------

@@ -33,3 +33,31 @@ class RMSNorm(Norm):
 
     def fused_decode_fields(self):
         return {"kind": "rmsnorm", "weight": self.weight, "eps": self.eps, "size": self.size}
+
+
+@register_norm("dynamic_tanh")
+class DynamicTanh(Norm):
+    """y = tanh(alpha * v) * weight + bias with v = residual + x in float32, element by element: a norm that takes no mean
+    and no variance of the row.  Tensors: the weight under `name` (default "<prefix>.weight"), the bias under "<name>.b" and
+    the scalar alpha under "<name>.alpha".  params: size, optional name."""
+
+    def __init__(self, spec, prefix, env):
+        super().__init__(spec, prefix, env)
+        self.size = int(spec["size"])
+        self.tensor_name = spec.get("name") or self.name("weight")
+        self.weight = self.bias = None
+        self.alpha = 1.0
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        return {self.tensor_name: TensorDecl((self.size,), kind="vector", init="norm"),
+                self.tensor_name + ".b": TensorDecl((self.size,), kind="vector"),
+                self.tensor_name + ".alpha": TensorDecl((), kind="vector", init="norm")}
+
+    def load(self, src) -> None:
+        self.weight = src.fetch(self.tensor_name).float().contiguous()
+        self.bias = src.fetch(self.tensor_name + ".b").float().contiguous()
+        self.alpha = float(src.fetch(self.tensor_name + ".alpha").float().item())
+
+    def forward(self, x=None, residual=None, residual_out=None, rows=None):
+        return ops.dyntanh(self.weight, self.bias, self.alpha, x=x, residual=residual, residual_out=residual_out, rows=rows,
+                           out_dtype=self.env.dtype)

@@ -38,13 +38,19 @@ class TensorDecl:
     kind: str = "matrix"
     init: str = "normal"          # "normal": N(0, std)   "norm": 1 + N(0, 0.05)   "zeros"
     optional: bool = False        # may be present and is then ignored (e.g. the head of a tied model)
+    std: Optional[float] = None   # spread of the random-weights mode for this tensor (default: the source's)
+    random_shape: Optional[Tuple[int, ...]] = None     # a dimension of `shape` that is -1 is whatever the checkpoint has;
+                                                        # the random-weights mode then draws this shape
 
 
 def check_index(expected: Dict[str, TensorDecl], index: Dict[str, TensorEntry], where: str) -> None:
     missing = [n for n, d in expected.items() if not d.optional and n not in index]
     unexpected = [n for n in index if n not in expected]
+    def fits(have, want) -> bool:
+        return len(have) == len(want) and all(w == -1 or h == w for h, w in zip(have, want))
+
     wrong = [(n, tuple(index[n].shape), tuple(d.shape)) for n, d in expected.items()
-             if n in index and not d.optional and tuple(index[n].shape) != tuple(d.shape)]
+             if n in index and not d.optional and not fits(tuple(index[n].shape), tuple(d.shape))]
     if not (missing or unexpected or wrong):
         return
     lines = [f"{where}: the tensors do not match the model described by config.json"]
@@ -105,11 +111,12 @@ class RandomSource:
         decl = self.expected[name]
         h = hashlib.sha256(f"{self.seed}:{name}".encode()).digest()
         g = torch.Generator(device=self.device).manual_seed(int.from_bytes(h[:7], "little"))
+        shape = decl.random_shape if decl.random_shape is not None else decl.shape
         if decl.kind == "int" or decl.init == "zeros":
-            return torch.zeros(decl.shape, dtype=torch.int32 if decl.kind == "int" else self.store_dtype,
+            return torch.zeros(shape, dtype=torch.int32 if decl.kind == "int" else self.store_dtype,
                                device=self.device)
-        t = torch.randn(decl.shape, generator=g, dtype=torch.float32, device=self.device)
-        t = 1.0 + 0.05 * t if decl.init == "norm" else self.std * t
+        t = torch.randn(shape, generator=g, dtype=torch.float32, device=self.device)
+        t = 1.0 + 0.05 * t if decl.init == "norm" else (decl.std if decl.std is not None else self.std) * t
         return t.to(self.store_dtype)
 
     def fetch(self, name: str) -> torch.Tensor:

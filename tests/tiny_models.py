@@ -133,7 +133,7 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor]) -> None:
     header, blobs, off = {}, [], 0
     for name in sorted(tensors):
         t = tensors[name].contiguous().cpu()
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[name] = {"dtype": _ST_DTYPES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
         blobs.append(raw)
         off += len(raw)

@@ -526,6 +526,115 @@ def workload_sweep(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# --workload vekurax_compare: the Vekurax design beside Qwen3 at equal layer sizes
+# ---------------------------------------------------------------------------------------------------------------------
+COMPARE_SIZES = {          # width, query heads, kv heads, head size, feed-forward width (the layer sizes of Qwen3-1.7B / 8B)
+    "1.7b": dict(width=2048, heads=16, kv_heads=8, dim=128, ff=6144),
+    "8b": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288),
+}
+
+
+def vekurax_config(size, layers, vocab, window=1024, keep_first=4):
+    """A Vekurax model with the given layer sizes: the windowed attention has the heads of the Qwen3 layer, the linear attention
+    half as many heads with key size 64 and value size 128, the feed-forward the same width; every layer has tensors of its own."""
+    s = COMPARE_SIZES[size]
+    r_heads = max(s["heads"] // 2, 1)
+    layer = {"type": "parallel",
+             "mixer": {"left": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "conv": 4,
+                                "bias_max": 2 * window, "scale": s["dim"] ** -0.5, "mask": {"size": window, "keep_first": keep_first}},
+                       "right": {"heads": r_heads, "dim": 64, "vdim": 128,
+                                 "decay": [1.0 - 2.0 ** (-3 - 5 * h / max(r_heads - 1, 1)) for h in range(r_heads)]},
+                       "left_scale": 0.8, "right_scale": 0.5},
+             "mlp": {"kind": "dense", "ff": s["ff"]}}
+    return {"architecture": "Vekurax", "width": s["width"], "vocab": vocab, "norm": {"eps": 1e-5}, "layers": [layer] * layers}
+
+
+def workload_vekurax(args):
+    """Prefill (one 2,048-token prompt a step) and decode (--batch requests at --context tokens, one token each a step through
+    the CUDA graph) of a Vekurax model and of a Qwen3 model with the same width, heads, feed-forward width, vocabulary and number
+    of layers (--layers, default 4; random weights), device-timed, with the mean time of every kernel of a step."""
+    import torch
+
+    from mini_sglang_b200 import Engine, EngineArgs
+    from mini_sglang_b200.engine.step import StepEntry
+
+    L = 4 if args.layers == FULL_LAYERS else args.layers
+    B, CTX, PAGE, PREFILL, V = args.batch, args.context, 16, 2048, 32768
+    W, K = max(args.warmup, 3), min(args.steps, 32)
+    pk = peaks()
+    clocks = ClockSampler()
+    clocks.start()
+    gen = torch.Generator().manual_seed(0)
+    rand = lambda n: torch.randint(0, V, (n,), generator=gen).tolist()      # noqa: E731
+    out = {"workload": "vekurax_compare", "layers": L, "batch": B, "context": CTX, "prefill_tokens": PREFILL, "vocab": V,
+           "dtype": "bf16", "data": "synthetic (random weights, random tokens)", "peaks": pk, "sizes": {}}
+    for size in (args.sizes.split(",") if args.sizes else list(COMPARE_SIZES)):
+        s = COMPARE_SIZES[size]
+        qwen = dict(QWEN3_8B, num_hidden_layers=L, hidden_size=s["width"], num_attention_heads=s["heads"],
+                    num_key_value_heads=s["kv_heads"], head_dim=s["dim"], intermediate_size=s["ff"], vocab_size=V,
+                    tie_word_embeddings=True, max_position_embeddings=CTX + 4096)
+        res = {}
+        for arch, cfg in (("vekurax", vekurax_config(size, L, V)), ("qwen3", qwen)):
+            tmp = tempfile.mkdtemp(prefix="msgl_bench_")
+            with open(os.path.join(tmp, "config.json"), "w") as f:
+                json.dump(cfg, f)
+            eng = Engine(EngineArgs(model=tmp, dummy_load=True, random_seed=0, page_size=PAGE, num_pages=(B + 1) * (CTX // PAGE + 8) + 256,
+                                    max_num_reqs=B + 2, max_context_len=CTX + 2048, max_prefill_tokens=8192, chunk_size=2048,
+                                    disable_radix_cache=True, schedule_policy="fcfs", log_level="WARNING"))
+            runner = eng.runner
+            toks = rand(PREFILL)
+
+            def prefill_step():
+                slot = runner.open()
+                runner.step([StepEntry(slot, toks, [PREFILL - 1])])
+                runner.close(slot)
+
+            for _ in range(W):
+                prefill_step()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(5):
+                prefill_step()
+            e1.record()
+            torch.cuda.synchronize()
+            pre_ms = e0.elapsed_time(e1) / 5
+            pre_kernels = profile_kernels(prefill_step, 2)
+            slots = [runner.open() for _ in range(B)]
+            for slot in slots:
+                ctx_toks = rand(CTX - (W + K) - 8)
+                for i in range(0, len(ctx_toks), 2048):
+                    runner.step([StepEntry(slot, ctx_toks[i:i + 2048], [])])
+
+            def decode_step():
+                runner.step([StepEntry(slot, rand(1), [0]) for slot in slots])
+
+            for _ in range(W):
+                decode_step()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(K):
+                decode_step()
+            e1.record()
+            torch.cuda.synchronize()
+            dec_ms = e0.elapsed_time(e1) / K
+            dec_kernels = profile_kernels(decode_step, 3, captures=lambda: len(runner._graphs))
+            res[arch] = {"prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(PREFILL / pre_ms * 1e3, 1),
+                         "decode_ms_per_step": round(dec_ms, 4), "decode_tok_s": round(B / dec_ms * 1e3, 1),
+                         "decode_graph": bool(runner.last_step_used_graph), "prefill_kernels": pre_kernels, "decode_kernels": dec_kernels}
+            for slot in slots:
+                runner.close(slot)
+            del eng, runner
+            torch.cuda.empty_cache()
+        out["sizes"][size] = res
+    clocks.stop()
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -541,8 +650,9 @@ def main():
     ap.add_argument("--profiler-range", action="store_true",
                     help="cudaProfilerStart/Stop around the timed region (ncu --profile-from-start off)")
     ap.add_argument("--no-graph", action="store_true", help="decode without CUDA graphs")
-    ap.add_argument("--workload", default="headline", choices=["headline", "qwen3_0.6b_mixed", "qwen3_32b_long", "sweep"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "qwen3_0.6b_mixed", "qwen3_32b_long", "sweep", "vekurax_compare"],
                     help="headline: the line the contract names; the others: further workloads, one JSON line each")
+    ap.add_argument("--sizes", default=None, help="--workload vekurax_compare: layer sizes to run, of " + ",".join(COMPARE_SIZES))
     ap.add_argument("--skip-sanity", action="store_true", help="no comparison with the plain implementation before timing")
     ap.add_argument("--model", default="8b", choices=["8b", "32b", "0.6b"], help="layer sizes for --only decode / prefill")
     ap.add_argument("--lengths", default=None,
@@ -562,6 +672,8 @@ def main():
         return workload_long(args)
     if args.workload == "sweep":
         return workload_sweep(args)
+    if args.workload == "vekurax_compare":
+        return workload_vekurax(args)
 
     import torch
 

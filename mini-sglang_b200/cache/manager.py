@@ -43,7 +43,9 @@ class PagedKVNeed:
     window: Optional[int] = None
     q_heads: int = 0                 # hint for work splitting only
     keep_first: int = 0              # with a window: the first tokens of a request stay readable too
-    library: Optional[str] = "attention"      # the kernel library that reads the cache (built before the first step)
+    library: Optional[str] = "attention"      # the kernel library that reads the cache (built before the first step);
+                                              # "attention": csrc/attention.cu, whose decode launches the step plans kv splits for
+    even_cut: bool = True            # whether a decode step may deal this cache's keys out evenly over the blocks
 
 
 @dataclasses.dataclass(frozen=True)

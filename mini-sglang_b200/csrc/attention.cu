@@ -70,6 +70,11 @@ struct AttnParams {
     float scale;
     int qlen_min, qlen_max;   // this launch takes the requests with qlen_min <= q_len <= qlen_max
     int uniform_decode;       // every request has exactly one token: tile index == request index
+    // with a window: the first keep_first keys of a request stay visible whatever the window (bfloat16 mma kernels)
+    int keep_first = 0;
+    // null, or [n_q][bias_len] float32 in log2 units: added to the scaled score by distance min(position - key, bias_len - 1)
+    const float* bias = nullptr;
+    int bias_len = 0;
 };
 
 // position -> (page index within the request, slot within the page)
@@ -155,6 +160,26 @@ __device__ __forceinline__ void block_place(const AttnParams& p, int& tile_idx, 
     }
 }
 
+// Kept first tokens that lie before the first key tile of the window: keys [0, sink_keys).  Split 0 reads them ahead of its
+// share of the window's tiles; they are no part of key_tile_range.
+__device__ __forceinline__ int sink_keys(const AttnParams& p, int p_min, int KT, int split) {
+    if (p.window <= 0 || p.keep_first <= 0 || split != 0) return 0;
+    const int k_lo = max(0, p_min - p.window + 1);
+    return min(p.keep_first, (k_lo / KT) * KT);
+}
+// whether the cache row of `key` may be read by a block whose queries sit at p_min..p_max: rows behind the window may lie
+// on pages that were given back
+__device__ __forceinline__ bool key_row_live(const AttnParams& p, int key, int p_min, int p_max) {
+    if (key > p_max) return false;
+    if (p.window <= 0) return true;
+    return key > p_min - p.window || key < p.keep_first;
+}
+__device__ __forceinline__ bool key_visible(const AttnParams& p, int key, int pos) {
+    bool ok = key <= pos;
+    if (p.window > 0) ok = ok && (key > pos - p.window || key < p.keep_first);
+    return ok;
+}
+
 // Which key tiles a block walks: the tiles that hold keys [k_lo, p_max], cut into ns splits.
 __device__ __forceinline__ void key_tile_range(const AttnParams& p, const TileInfo& ti, int KT, int split, int ns,
                                                int& p_min, int& p_max, int& kt_begin, int& kt_end) {
@@ -227,7 +252,7 @@ constexpr int MMA_KT = 64;        // keys per tile
 constexpr int MMA_WARPS = 4;
 constexpr int MMA_THREADS = MMA_WARPS * 32;
 
-template <int D>
+template <int D, bool EXT = false>
 __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams p) {
     constexpr int R = 64;                           // rows per block
     constexpr int LDS = D + 8;                      // padded row of a shared-memory tile (elements)
@@ -279,9 +304,16 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
     // a thread copies half a row of K and of V per tile: row tid / 2, 16-byte chunks 2j + (tid & 1);
     // the row's page is looked up once per tile, one tile ahead of the copy that needs it
     const int ld_row = tid >> 1, ld_half = tid & 1;
-    auto tile_page = [&](int kt) -> int {
-        const int key = kt * MMA_KT + ld_row;
-        return (kt < kt_end && key <= p_max) ? bt[page_index(p, key)] : -1;
+    // iterations: first the tiles of the kept first tokens before the window (split 0 only), then the split's own tiles
+    const int sink_hi = EXT ? sink_keys(p, p_min, MMA_KT, split) : 0;
+    const int n_sink_t = (sink_hi + MMA_KT - 1) / MMA_KT;
+    const int n_tiles = n_sink_t + (kt_end - kt_begin);
+    auto tile_of = [&](int it) -> int { return it < n_sink_t ? it : kt_begin + (it - n_sink_t); };
+    auto tile_page = [&](int it) -> int {
+        if (it >= n_tiles) return -1;
+        const int key = tile_of(it) * MMA_KT + ld_row;
+        const bool live = !EXT ? key <= p_max : (it < n_sink_t ? key < sink_hi : key_row_live(p, key, p_min, p_max));
+        return live ? bt[page_index(p, key)] : -1;
     };
     constexpr unsigned STAGE_BYTES = 2u * MMA_KT * LDS * 2u, TILE_BYTES = MMA_KT * LDS * 2u;
     const unsigned q_s = smem_u32(Qs), kv_s = smem_u32(KVs);
@@ -317,17 +349,24 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
     for (int i = 0; i < NDB; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
 
-    const int n_tiles = kt_end - kt_begin;
-    if (n_tiles > 0) load_kv(0, kt_begin, tile_page(kt_begin));
+    if (n_tiles > 0) load_kv(0, tile_of(0), tile_page(0));
     cp_async_commit();
-    int pg_next = tile_page(kt_begin + 1);
+    int pg_next = tile_page(1);
+    // the distance bias of the two rows' heads (rows without a head read the last head's table; their results are dropped)
+    const float* bias_lo = nullptr;
+    const float* bias_hi = nullptr;
+    if (EXT && p.bias) {
+        bias_lo = p.bias + (size_t)min(kvh * G + chunk * R + (r_lo - (r_lo / Gc) * Gc), p.n_q - 1) * p.bias_len;
+        bias_hi = p.bias + (size_t)min(kvh * G + chunk * R + (r_hi - (r_hi / Gc) * Gc), p.n_q - 1) * p.bias_len;
+    }
+    const float sc_exp = (EXT && p.bias) ? 1.f : sc;          // with a bias the scores are brought to log2 units where it is added
 
     for (int it = 0; it < n_tiles; ++it) {
-        const int kt = kt_begin + it;
+        const int kt = tile_of(it);
         if (it + 1 < n_tiles) {
-            load_kv((it + 1) & 1, kt + 1, pg_next);
+            load_kv((it + 1) & 1, tile_of(it + 1), pg_next);
             cp_async_commit();
-            pg_next = tile_page(kt + 2);
+            pg_next = tile_page(it + 2);
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
@@ -354,7 +393,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
 
         // ---- scale, mask, online softmax
         const int key0 = kt * MMA_KT + key_base;
-        const bool need_mask = (kt * MMA_KT + MMA_KT - 1 > p_min) ||
+        const bool need_mask = (kt * MMA_KT + MMA_KT - 1 > p_min) || it < n_sink_t ||
                                (p.window > 0 && kt * MMA_KT <= p_max - p.window);
         // raw scores stay unscaled: the scale is folded into the exponent, 2^(s * sc - m)
         float mx_lo = -INFINITY, mx_hi = -INFINITY;
@@ -363,12 +402,18 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 float v = s[nb][e];
-                if (need_mask) {
+                if (need_mask || (EXT && p.bias)) {
                     const int key = key0 + nb * 8 + (lane & 3) * 2 + (e & 1);
                     const int pos = (e < 2) ? pos_lo : pos_hi;
-                    bool ok = key <= pos;
-                    if (p.window > 0) ok = ok && (key > pos - p.window);
+                    bool ok;
+                    if (EXT) {
+                        ok = !need_mask || (key_visible(p, key, pos) && (it >= n_sink_t || key < sink_hi));
+                    } else {
+                        ok = key <= pos;
+                        if (p.window > 0) ok = ok && (key > pos - p.window);
+                    }
                     if (!ok) v = -INFINITY;
+                    else if (EXT && p.bias) v = fmaf(v, sc, ((e < 2) ? bias_lo : bias_hi)[min(max(pos - key, 0), p.bias_len - 1)]);
                     s[nb][e] = v;
                 }
                 if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
@@ -378,15 +423,15 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
         mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
         mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
         mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-        const float mn_lo = fmaxf(m_lo, mx_lo * sc), mn_hi = fmaxf(m_hi, mx_hi * sc);       // -inf * sc = -inf (sc > 0)
+        const float mn_lo = fmaxf(m_lo, mx_lo * sc_exp), mn_hi = fmaxf(m_hi, mx_hi * sc_exp);       // -inf * sc = -inf (sc > 0)
         const float mu_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo, mu_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
         const float al_lo = fast_exp2(m_lo - mu_lo), al_hi = fast_exp2(m_hi - mu_hi);
         m_lo = mn_lo; m_hi = mn_hi;
         l_lo *= al_lo; l_hi *= al_hi;
 #pragma unroll
         for (int nb = 0; nb < NKB; ++nb) {
-            s[nb][0] = fast_exp2(fmaf(s[nb][0], sc, -mu_lo)); s[nb][1] = fast_exp2(fmaf(s[nb][1], sc, -mu_lo));
-            s[nb][2] = fast_exp2(fmaf(s[nb][2], sc, -mu_hi)); s[nb][3] = fast_exp2(fmaf(s[nb][3], sc, -mu_hi));
+            s[nb][0] = fast_exp2(fmaf(s[nb][0], sc_exp, -mu_lo)); s[nb][1] = fast_exp2(fmaf(s[nb][1], sc_exp, -mu_lo));
+            s[nb][2] = fast_exp2(fmaf(s[nb][2], sc_exp, -mu_hi)); s[nb][3] = fast_exp2(fmaf(s[nb][3], sc_exp, -mu_hi));
             l_lo += s[nb][0] + s[nb][1];
             l_hi += s[nb][2] + s[nb][3];
         }
@@ -730,10 +775,11 @@ __device__ __forceinline__ uint4 ldg16_stream(const void* ptr) {
 // warps taking them in turn; the result goes to the output (ns == 1) or to piece `split` of the request's partial results.
 // wait_here: this is the block's first run, the wait for the kernel before this one falls behind its first prefetches;
 // release_here: it is the last one, the next kernel may start beside its reduction.
-template <int D, int NW, int ST, int NBH>
+// EXT: the launch has kept first tokens or a distance bias (AttnParams::keep_first, bias); without it none of that is compiled in.
+template <int D, int NW, int ST, int NBH, bool EXT = false>
 __device__ __forceinline__ void decode_t_run(const AttnParams& p, const TileInfo& ti, int ns, int split, int u_begin, int u_end,
                                              int p_min, int p_max, int kvh, int chunk, bool wait_here, bool release_here,
-                                             __nv_bfloat16* ring) {
+                                             __nv_bfloat16* ring, int sink_hi = 0) {
     constexpr int LDS = D + 8;
     constexpr int C = 8 * NBH;                      // (token, head) columns per block
     constexpr int KP = D / 32;                      // 32-element groups of the head size
@@ -758,18 +804,36 @@ __device__ __forceinline__ void decode_t_run(const AttnParams& p, const TileInfo
 #pragma unroll
         for (int e = 0; e < 2; ++e) pos_c[nb][e] = p_min + (nb * 8 + 2 * t + e) / Gc;
 
-    const int n_my = (u_end - u_begin > warp) ? (u_end - u_begin - warp + NW - 1) / NW : 0;
+    // the units of the kept first tokens before the window (keys [0, sink_hi)) come first, then units [u_begin, u_end)
+    const int n_su = EXT ? (sink_hi + DEC_WT - 1) / DEC_WT : 0;
+    const int n_units = n_su + (u_end - u_begin);
+    const int n_my = (n_units > warp) ? (n_units - warp + NW - 1) / NW : 0;
+    auto unit_of = [&](int i) -> int { const int lu = warp + i * NW; return lu < n_su ? lu : u_begin + (lu - n_su); };
+    auto row_live = [&](int i, int key) -> bool {
+        if (!EXT) return key <= p_max;
+        return (warp + i * NW < n_su) ? key < sink_hi : key_row_live(p, key, p_min, p_max);
+    };
+    // bias tables of the columns this lane sees
+    const float* bias_c[NBH][2];
+#pragma unroll
+    for (int nb = 0; nb < NBH; ++nb)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int c = nb * 8 + 2 * t + e;
+            const int head = min(kvh * G + chunk * C + (c - (c / Gc) * Gc), p.n_q - 1);
+            bias_c[nb][e] = (EXT && p.bias) ? p.bias + (size_t)head * p.bias_len : nullptr;
+        }
     __nv_bfloat16* my_ring = ring + (size_t)warp * ST * DEC_WT * LDS;
     const int v_key = lane >> 1, v_half = lane & 1;
 
     // page of key (unit i, row lane & 15), or -1 past the last key; one lookup per lane and unit
     auto unit_page = [&](int i) -> int {
-        const int key = (u_begin + warp + i * NW) * DEC_WT + (lane & 15);
-        return (i < n_my && key <= p_max) ? bt[page_index(p, key)] : -1;
+        const int key = unit_of(i) * DEC_WT + (lane & 15);
+        return (i < n_my && row_live(i, key)) ? bt[page_index(p, key)] : -1;
     };
     auto load_v = [&](int i, int pg_row) {         // V of unit i -> stage i % ST; pg_row: page of row v_key
         __nv_bfloat16* Vs = my_ring + (size_t)(i % ST) * DEC_WT * LDS;
-        const int key = (u_begin + warp + i * NW) * DEC_WT + v_key;
+        const int key = unit_of(i) * DEC_WT + v_key;
         const bool valid = pg_row >= 0;
         size_t off = 0;
         if (valid) off = (((size_t)pg_row * p.n_kv + kvh) * p.page_size + page_slot(p, key)) * D;
@@ -783,7 +847,7 @@ __device__ __forceinline__ void decode_t_run(const AttnParams& p, const TileInfo
     // pg_row: page of row lane >> 1, each lane touches 128-byte lines of that row
     auto prefetch_k = [&](int i, int pg_row) {
         if (pg_row < 0) return;
-        const int key = (u_begin + warp + i * NW) * DEC_WT + v_key;
+        const int key = unit_of(i) * DEC_WT + v_key;
         const size_t off = (((size_t)pg_row * p.n_kv + kvh) * p.page_size + page_slot(p, key)) * D;
 #pragma unroll
         for (int ln = 0; ln < (D + 127) / 128; ++ln) {
@@ -798,7 +862,7 @@ __device__ __forceinline__ void decode_t_run(const AttnParams& p, const TileInfo
     };
     uint4 k_lo[KP], k_hi[KP];
     auto load_k = [&](int i, int pg_lo, int pg_hi) {      // K of unit i -> registers (rows g and g + 8)
-        const int key0 = (u_begin + warp + i * NW) * DEC_WT;
+        const int key0 = unit_of(i) * DEC_WT;
         const __nv_bfloat16* lo = kc + (((size_t)max(pg_lo, 0) * p.n_kv + kvh) * p.page_size + page_slot(p, key0 + g)) * D + 8 * t;
         const __nv_bfloat16* hi = kc + (((size_t)max(pg_hi, 0) * p.n_kv + kvh) * p.page_size + page_slot(p, key0 + 8 + g)) * D + 8 * t;
 #pragma unroll
@@ -886,8 +950,9 @@ __device__ __forceinline__ void decode_t_run(const AttnParams& p, const TileInfo
             pg_v_next = unit_page(i + ST);
         }
         // ---- scale, mask, online softmax per column
-        const int key0 = (u_begin + warp + i * NW) * DEC_WT;
-        const bool need_mask = (key0 + DEC_WT - 1 > p_min) || (p.window > 0 && key0 <= p_max - p.window);
+        const int key0 = unit_of(i) * DEC_WT;
+        const bool in_sink = EXT && warp + i * NW < n_su;
+        const bool need_mask = in_sink || (key0 + DEC_WT - 1 > p_min) || (p.window > 0 && key0 <= p_max - p.window);
         unsigned pb0[NBH], pb1[NBH];
         float v[NBH][4];
         bool behind = false;              // a score lies further above its column's reference than DEC_LAZY allows
@@ -896,12 +961,18 @@ __device__ __forceinline__ void decode_t_run(const AttnParams& p, const TileInfo
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 v[nb][e] = (s[nb][e] + s2[nb][e]) * sc;
-                if (need_mask) {
+                if (need_mask || (EXT && p.bias)) {
                     const int key = key0 + g + ((e & 2) ? 8 : 0);
                     const int pos = pos_c[nb][e & 1];
-                    bool ok = key <= pos;
-                    if (p.window > 0) ok = ok && (key > pos - p.window);
+                    bool ok;
+                    if (EXT) {
+                        ok = !need_mask || (key_visible(p, key, pos) && (!in_sink || key < sink_hi));
+                    } else {
+                        ok = key <= pos;
+                        if (p.window > 0) ok = ok && (key > pos - p.window);
+                    }
                     if (!ok) v[nb][e] = -INFINITY;
+                    else if (EXT && p.bias) v[nb][e] += bias_c[nb][e & 1][min(max(pos - key, 0), p.bias_len - 1)];
                 }
                 behind = behind || v[nb][e] > m_c[nb][e & 1] + DEC_LAZY;
             }
@@ -1027,7 +1098,7 @@ __device__ __forceinline__ void decode_t_run(const AttnParams& p, const TileInfo
     }
 }
 
-template <int D, int NW, int ST, int NBH>
+template <int D, int NW, int ST, int NBH, bool EXT = false>
 __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_decode_t_kernel(const AttnParams p) {
     constexpr int C = 8 * NBH;
     static_assert(D % 32 == 0, "the transposed decode kernel needs head sizes in steps of 32");
@@ -1058,7 +1129,8 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
     key_tile_range(p, ti, MMA_KT, split, ns, p_min, p_max, kt_begin, kt_end);
     const int u_begin = kt_begin * (MMA_KT / DEC_WT);
     const int u_end = min(kt_end * (MMA_KT / DEC_WT), p_max / DEC_WT + 1);
-    decode_t_run<D, NW, ST, NBH>(p, ti, ns, split, u_begin, u_end, p_min, p_max, kvh, chunk, true, true, ring);
+    decode_t_run<D, NW, ST, NBH, EXT>(p, ti, ns, split, u_begin, u_end, p_min, p_max, kvh, chunk, true, true, ring,
+                                      EXT ? sink_keys(p, p_min, MMA_KT, split) : 0);
 }
 
 // The same arithmetic for a decode step (one token a request) with the keys of all requests dealt out evenly: the launch
@@ -1329,12 +1401,47 @@ template <int D> static size_t mma_smem_bytes() {
 }
 
 // grid_x: number of query tiles the launch has to cover (the host knows every q_len).
+static int attention_launch(const void* q, void* out, const void* k_cache, const void* v_cache, const int* q_start,
+                            const int* kv_len, const int* block_table, const int* nsplit, float* part_o,
+                            float* part_ml, int B, int T_, int n_q, int n_kv, int d, int page_size, int bt_stride,
+                            int window, int max_split, float scale, int qlen_min, int qlen_max, int uniform_decode,
+                            int variant, int grid_x, int dtype, const int* order, const int* even, int even_nb,
+                            int keep_first, const float* bias, int bias_len, cudaStream_t stream);
+
 MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const void* v_cache, const int* q_start,
                             const int* kv_len, const int* block_table, const int* nsplit, float* part_o,
                             float* part_ml, int B, int T_, int n_q, int n_kv, int d, int page_size, int bt_stride,
                             int window, int max_split, float scale, int qlen_min, int qlen_max, int uniform_decode,
                             int variant, int grid_x, int dtype, const int* order, const int* even, int even_nb,
                             cudaStream_t stream) {
+    return attention_launch(q, out, k_cache, v_cache, q_start, kv_len, block_table, nsplit, part_o, part_ml, B, T_, n_q, n_kv, d,
+                            page_size, bt_stride, window, max_split, scale, qlen_min, qlen_max, uniform_decode, variant, grid_x,
+                            dtype, order, even, even_nb, 0, nullptr, 0, stream);
+}
+
+// The same with a window that keeps the first `keep_first` keys of every request visible and with a bias by distance
+// (`bias`: [n_q][bias_len] float32 in log2 units, or null).  Taken by the bfloat16 mma kernels: variant 1, and variant 2
+// for head sizes in steps of 32 with up to 16 query heads a kv head; anything else is refused.
+MSGL_API int msgl_attention_window(const void* q, void* out, const void* k_cache, const void* v_cache, const int* q_start,
+                                   const int* kv_len, const int* block_table, const int* nsplit, float* part_o,
+                                   float* part_ml, int B, int T_, int n_q, int n_kv, int d, int page_size, int bt_stride,
+                                   int window, int max_split, float scale, int qlen_min, int qlen_max, int uniform_decode,
+                                   int variant, int grid_x, int dtype, const int* order, int keep_first, const float* bias,
+                                   int bias_len, cudaStream_t stream) {
+    if (keep_first < 0 || (bias != nullptr && bias_len < 1)) return MSGL_ERR_SIZE;
+    const int G = n_kv > 0 ? n_q / n_kv : 0;
+    if (!(variant == 1 || (variant == 2 && MSGL_HEAD_DIM % 32 == 0 && G <= 16))) return MSGL_ERR_SIZE;
+    return attention_launch(q, out, k_cache, v_cache, q_start, kv_len, block_table, nsplit, part_o, part_ml, B, T_, n_q, n_kv, d,
+                            page_size, bt_stride, window, max_split, scale, qlen_min, qlen_max, uniform_decode, variant, grid_x,
+                            dtype, order, nullptr, 0, keep_first, bias, bias_len, stream);
+}
+
+static int attention_launch(const void* q, void* out, const void* k_cache, const void* v_cache, const int* q_start,
+                            const int* kv_len, const int* block_table, const int* nsplit, float* part_o,
+                            float* part_ml, int B, int T_, int n_q, int n_kv, int d, int page_size, int bt_stride,
+                            int window, int max_split, float scale, int qlen_min, int qlen_max, int uniform_decode,
+                            int variant, int grid_x, int dtype, const int* order, const int* even, int even_nb,
+                            int keep_first, const float* bias, int bias_len, cudaStream_t stream) {
     if (grid_x <= 0 || B <= 0) return MSGL_OK;
     if (n_kv <= 0 || n_q % n_kv != 0 || d <= 0 || page_size <= 0 || max_split < 1) return MSGL_ERR_SIZE;
     if (max_split > 1 && (part_o == nullptr || part_ml == nullptr || nsplit == nullptr)) return MSGL_ERR_SIZE;
@@ -1347,6 +1454,7 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
     p.page_shift = -1;
     if ((page_size & (page_size - 1)) == 0) { int sh = 0; while ((1 << sh) < page_size) ++sh; p.page_shift = sh; } p.scale = scale; p.qlen_min = qlen_min; p.qlen_max = qlen_max;
     p.uniform_decode = uniform_decode;
+    p.keep_first = window > 0 ? keep_first : 0; p.bias = bias; p.bias_len = bias_len;
     const int G = n_q / n_kv;
     const int R = variant == 1 ? 64 : 16;
     const int n_chunks = G <= R ? 1 : (G + R - 1) / R;
@@ -1384,9 +1492,11 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
         static MsglOncePerDevice attr_set;   // set once per device, outside any stream capture (the first launch is never captured)
         if (attr_set.due()) {
             cudaFuncSetAttribute(attn_mma_kernel<MSGL_HEAD_DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaFuncSetAttribute(attn_mma_kernel<MSGL_HEAD_DIM, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             attr_set.mark();
         }
-        attn_mma_kernel<MSGL_HEAD_DIM><<<grid, MMA_THREADS, smem, stream>>>(p);
+        if (p.keep_first > 0 || p.bias != nullptr) attn_mma_kernel<MSGL_HEAD_DIM, true><<<grid, MMA_THREADS, smem, stream>>>(p);
+        else attn_mma_kernel<MSGL_HEAD_DIM><<<grid, MMA_THREADS, smem, stream>>>(p);
     } else if (variant == 2) {
         constexpr int NW = MSGL_DEC_WARPS;
         if (MSGL_HEAD_DIM % 32 == 0 && G <= 16) {
@@ -1400,6 +1510,8 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
             if (attr_set.due()) {
                 cudaFuncSetAttribute(attn_decode_t_kernel<DT, NW, ST, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 cudaFuncSetAttribute(attn_decode_t_kernel<DT, NW, ST, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                cudaFuncSetAttribute(attn_decode_t_kernel<DT, NW, ST, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                cudaFuncSetAttribute(attn_decode_t_kernel<DT, NW, ST, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 cudaFuncSetAttribute(attn_decode_even_kernel<DT, NW, ST, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 cudaFuncSetAttribute(attn_decode_even_kernel<DT, NW, ST, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 attr_set.mark();
@@ -1413,7 +1525,10 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
                 else msgl_launch_pdl(attn_decode_even_kernel<DT, NW, ST, 2>, grid, dim3(NW * 32), smem, stream, p);
                 return msgl_check_launch();
             }
-            if (C == 8) msgl_launch_pdl(attn_decode_t_kernel<DT, NW, ST, 1>, grid, dim3(NW * 32), smem, stream, p);
+            const bool ext = p.keep_first > 0 || p.bias != nullptr;
+            if (ext && C == 8) msgl_launch_pdl(attn_decode_t_kernel<DT, NW, ST, 1, true>, grid, dim3(NW * 32), smem, stream, p);
+            else if (ext) msgl_launch_pdl(attn_decode_t_kernel<DT, NW, ST, 2, true>, grid, dim3(NW * 32), smem, stream, p);
+            else if (C == 8) msgl_launch_pdl(attn_decode_t_kernel<DT, NW, ST, 1>, grid, dim3(NW * 32), smem, stream, p);
             else msgl_launch_pdl(attn_decode_t_kernel<DT, NW, ST, 2>, grid, dim3(NW * 32), smem, stream, p);
         } else {
             constexpr int ST = (MSGL_HEAD_DIM <= 128) ? MSGL_DEC_STAGES : 2;   // the ring must fit 227 KB

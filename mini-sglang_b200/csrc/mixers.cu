@@ -12,6 +12,7 @@
 //   decay_chunk_*_kernel        the same for long portions: chunks of a request in parallel, their sums scanned in order
 //   rms_gate_kernel             RMS norm over a row, times sigmoid(gate), times a constant
 //   gated_act_kernel            act(gate) * up with act = silu or tanh-gelu
+//   head_gate_kernel            a head's output times the sigmoid of the head's gate, into packed rows
 //
 // Element type T (float or bfloat16) is the type of activations and caches; every sum, norm, score, weight of the
 // softmax, decay and state is float32 in both.  Inputs that come out of a packed projection are addressed by a base
@@ -499,6 +500,241 @@ MSGL_API int msgl_decay_attention(const void* proj, long long stride, int q_off,
 }
 
 // ---------------------------------------------------------------------------------------
+// The same linear attention for long portions: a request's tokens of the step in chunks of 64, the chunks in parallel.
+// With L tokens in a chunk (local index i), a the head's decay and S the state before the chunk:
+//
+//   1. decay_chunk_kv_kernel    U = sum_i a^(L-1-i) k_i v_i^T                      every chunk by itself
+//   2. decay_chunk_scan_kernel  per request, chunk after chunk: U <- S (the state before the chunk), S <- a^L S + U;
+//                               the request's state row gets the last S
+//   3. decay_chunk_out_kernel   o_i = a^(i+1) S^T q_i + sum_{j<=i} a^(i-j) (q_i . k_j) v_j
+//
+// All products are float32 FMA on 64 x 64 tiles through shared memory, 4 x 4 results a thread.
+// ---------------------------------------------------------------------------------------
+#define DC_C 64
+#define DC_LD 65
+
+struct DecayChunkParams {
+    const void* proj; long long stride; int q_off, k_off, v_off;
+    int heads, dk, dv, B;
+    const float* decay; float* state; const int* q_start; const int* slots;
+    float* U;       // [chunks][heads][dk][dv]
+    float* out;     // [T][heads * dv]
+};
+
+__device__ __forceinline__ float dc_pow(float log2a, int n) { return n == 0 ? 1.f : exp2f((float)n * log2a); }
+
+// chunk index -> (request, first token of the chunk among the step's tokens, tokens in the chunk); false: no such chunk
+__device__ __forceinline__ bool dc_find_chunk(const DecayChunkParams& p, int chunk, int* sh, int& req, int& t0, int& L) {
+    if (threadIdx.x == 0) {
+        int left = chunk, found = -1, c0 = 0;
+        for (int r = 0; r < p.B; ++r) {
+            const int nc = (p.q_start[r + 1] - p.q_start[r] + DC_C - 1) / DC_C;
+            if (left < nc) { found = r; c0 = left * DC_C; break; }
+            left -= nc;
+        }
+        sh[0] = found; sh[1] = c0;
+    }
+    __syncthreads();
+    req = sh[0];
+    if (req < 0) return false;
+    const int base = p.q_start[req], n = p.q_start[req + 1] - base;
+    t0 = base + sh[1];
+    L = min(DC_C, n - sh[1]);
+    return true;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) decay_chunk_kv_kernel(const DecayChunkParams p) {
+    __shared__ __align__(16) float Ks[DC_C][64];
+    __shared__ __align__(16) float Vs[DC_C][64];
+    __shared__ int sh[2];
+    const int chunk = blockIdx.x, h = blockIdx.y;
+    const int n_ct = (p.dv + 63) / 64;
+    const int row0 = (blockIdx.z / n_ct) * 64, col0 = (blockIdx.z % n_ct) * 64;
+    int req, t0, L;
+    if (!dc_find_chunk(p, chunk, sh, req, t0, L)) return;
+    const float la = log2f(p.decay[h]);
+    const T* proj = reinterpret_cast<const T*>(p.proj);
+    const int tid = threadIdx.x;
+    for (int idx = tid; idx < DC_C * 64; idx += 256) {
+        const int i = idx >> 6, m = idx & 63;
+        float kv = 0.f, vv = 0.f;
+        if (i < L) {
+            const size_t row = (size_t)(t0 + i) * p.stride;
+            if (row0 + m < p.dk) kv = siluf_(to_f32<T>(proj[row + p.k_off + h * p.dk + row0 + m])) * dc_pow(la, L - 1 - i);
+            if (col0 + m < p.dv) vv = siluf_(to_f32<T>(proj[row + p.v_off + h * p.dv + col0 + m]));
+        }
+        Ks[i][m] = kv;
+        Vs[i][m] = vv;
+    }
+    __syncthreads();
+    const int ty = tid >> 4, tx = tid & 15;
+    float acc[4][4] = {};
+    for (int i = 0; i < L; ++i) {
+        const float4 kr = *reinterpret_cast<const float4*>(&Ks[i][ty * 4]);
+        const float4 vr = *reinterpret_cast<const float4*>(&Vs[i][tx * 4]);
+        const float ka[4] = {kr.x, kr.y, kr.z, kr.w}, va[4] = {vr.x, vr.y, vr.z, vr.w};
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(ka[a], va[b], acc[a][b]);
+    }
+    float* U = p.U + ((size_t)chunk * p.heads + h) * p.dk * p.dv;
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int row = row0 + ty * 4 + a;
+        if (row >= p.dk) continue;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int col = col0 + tx * 4 + b;
+            if (col < p.dv) U[(size_t)row * p.dv + col] = acc[a][b];
+        }
+    }
+}
+
+__global__ void decay_chunk_scan_kernel(const DecayChunkParams p) {
+    const int r = blockIdx.x, h = blockIdx.y;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    const int E = p.dk * p.dv;
+    if (e >= E) return;
+    const int n = p.q_start[r + 1] - p.q_start[r];
+    if (n <= 0) return;
+    int chunk0 = 0;
+    for (int r2 = 0; r2 < r; ++r2) chunk0 += (p.q_start[r2 + 1] - p.q_start[r2] + DC_C - 1) / DC_C;
+    const float la = log2f(p.decay[h]);
+    float* st = p.state + ((size_t)p.slots[r] * p.heads + h) * E + e;
+    float S = *st;
+    const int nc = (n + DC_C - 1) / DC_C;
+    for (int c = 0; c < nc; ++c) {
+        const int L = min(DC_C, n - c * DC_C);
+        float* u = p.U + ((size_t)(chunk0 + c) * p.heads + h) * E + e;
+        const float uv = *u;
+        *u = S;
+        S = fmaf(dc_pow(la, L), S, uv);
+    }
+    *st = S;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) decay_chunk_out_kernel(const DecayChunkParams p) {
+    __shared__ __align__(16) float As[DC_C][DC_LD];       // q slab; then v
+    __shared__ __align__(16) float Bs[DC_C][DC_LD];       // k slab; then the chunk's weights P; then a slab of S
+    __shared__ int sh[2];
+    const int chunk = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * 64;
+    int req, t0, L;
+    if (!dc_find_chunk(p, chunk, sh, req, t0, L)) return;
+    const float la = log2f(p.decay[h]);
+    const T* proj = reinterpret_cast<const T*>(p.proj);
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+
+    // ---- P[i][j] = a^(i-j) q_i . k_j for j <= i
+    float pacc[4][4] = {};
+    for (int m0 = 0; m0 < p.dk; m0 += 64) {
+        __syncthreads();
+        for (int idx = tid; idx < DC_C * 64; idx += 256) {
+            const int i = idx >> 6, m = idx & 63;
+            float qv = 0.f, kv = 0.f;
+            if (i < L && m0 + m < p.dk) {
+                const size_t row = (size_t)(t0 + i) * p.stride;
+                qv = siluf_(to_f32<T>(proj[row + p.q_off + h * p.dk + m0 + m]));
+                kv = siluf_(to_f32<T>(proj[row + p.k_off + h * p.dk + m0 + m]));
+            }
+            As[i][m] = qv;
+            Bs[i][m] = kv;
+        }
+        __syncthreads();
+        for (int m = 0; m < 64; ++m) {
+            float qa[4], kb[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) { qa[a] = As[ty * 4 + a][m]; kb[a] = Bs[tx * 4 + a][m]; }
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) pacc[a][b] = fmaf(qa[a], kb[b], pacc[a][b]);
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int i = ty * 4 + a, j = tx * 4 + b;
+            Bs[i][j] = (j <= i && i < L) ? pacc[a][b] * dc_pow(la, i - j) : 0.f;
+        }
+    for (int idx = tid; idx < DC_C * 64; idx += 256) {
+        const int j = idx >> 6, nn = idx & 63;
+        float vv = 0.f;
+        if (j < L && col0 + nn < p.dv) vv = siluf_(to_f32<T>(proj[(size_t)(t0 + j) * p.stride + p.v_off + h * p.dv + col0 + nn]));
+        As[j][nn] = vv;
+    }
+    __syncthreads();
+    // ---- O = P V
+    float oacc[4][4] = {};
+    for (int j = 0; j < L; ++j) {
+        float pa[4], vb[4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) { pa[a] = Bs[ty * 4 + a][j]; vb[a] = As[j][tx * 4 + a]; }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) oacc[a][b] = fmaf(pa[a], vb[b], oacc[a][b]);
+    }
+    // ---- O += diag(a^(i+1)) Q S, S the state before the chunk
+    const float* S = p.U + ((size_t)chunk * p.heads + h) * p.dk * p.dv;
+    for (int m0 = 0; m0 < p.dk; m0 += 64) {
+        __syncthreads();
+        for (int idx = tid; idx < DC_C * 64; idx += 256) {
+            const int i = idx >> 6, m = idx & 63;
+            float qv = 0.f;
+            if (i < L && m0 + m < p.dk)
+                qv = siluf_(to_f32<T>(proj[(size_t)(t0 + i) * p.stride + p.q_off + h * p.dk + m0 + m])) * dc_pow(la, i + 1);
+            As[i][m] = qv;
+            float sv = 0.f;                        // here i is the state's row within the slab, m its column
+            if (m0 + i < p.dk && col0 + m < p.dv) sv = S[(size_t)(m0 + i) * p.dv + col0 + m];
+            Bs[i][m] = sv;
+        }
+        __syncthreads();
+        for (int m = 0; m < 64; ++m) {
+            float qa[4], sb[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) { qa[a] = As[ty * 4 + a][m]; sb[a] = Bs[m][tx * 4 + a]; }
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) oacc[a][b] = fmaf(qa[a], sb[b], oacc[a][b]);
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int i = ty * 4 + a;
+        if (i >= L) continue;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int col = col0 + tx * 4 + b;
+            if (col < p.dv) p.out[(size_t)(t0 + i) * p.heads * p.dv + h * p.dv + col] = oacc[a][b];
+        }
+    }
+}
+
+MSGL_API int msgl_decay_attention_chunked(const void* proj, long long stride, int q_off, int k_off, int v_off, int heads, int dk,
+                                          int dv, const float* decay, float* state, const int* q_start, const int* slots,
+                                          float* out, float* U, int n_chunks, int B, int dtype, cudaStream_t stream) {
+    if (B <= 0 || n_chunks <= 0) return MSGL_OK;
+    if (heads <= 0 || dk <= 0 || dv <= 0) return MSGL_ERR_SIZE;
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    DecayChunkParams p;
+    p.proj = proj; p.stride = stride; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.heads = heads; p.dk = dk; p.dv = dv;
+    p.B = B; p.decay = decay; p.state = state; p.q_start = q_start; p.slots = slots; p.U = U; p.out = out;
+    const int n_rt = (dk + 63) / 64, n_ct = (dv + 63) / 64;
+    if (dtype == MSGL_F32) decay_chunk_kv_kernel<float><<<dim3(n_chunks, heads, n_rt * n_ct), 256, 0, stream>>>(p);
+    else decay_chunk_kv_kernel<__nv_bfloat16><<<dim3(n_chunks, heads, n_rt * n_ct), 256, 0, stream>>>(p);
+    decay_chunk_scan_kernel<<<dim3(B, heads, (dk * dv + 255) / 256), 256, 0, stream>>>(p);
+    if (dtype == MSGL_F32) decay_chunk_out_kernel<float><<<dim3(n_chunks, heads, n_ct), 256, 0, stream>>>(p);
+    else decay_chunk_out_kernel<__nv_bfloat16><<<dim3(n_chunks, heads, n_ct), 256, 0, stream>>>(p);
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
 // y = x / sqrt(mean(x^2) + eps) * w * sigmoid(gate) * c   (x float32 [T, N]; gate and y in packed rows)
 // ---------------------------------------------------------------------------------------
 template <typename T>
@@ -539,27 +775,57 @@ MSGL_API int msgl_rms_gate(const float* x, int N, const float* w, float eps, con
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void gated_act_kernel(const void* in_, long long in_stride, int gate_off, int up_off, void* out_, long long out_stride,
-                                 int out_off, int I, int act, long long total) {
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= total) return;
-    const long long t = idx / I;
-    const int i = (int)(idx - t * I);
+                                 int out_off, int I, int act) {
+    const long long t = blockIdx.y;
     const T* in = reinterpret_cast<const T*>(in_) + t * in_stride;
-    const float g = to_f32<T>(in[gate_off + i]), u = to_f32<T>(in[up_off + i]);
-    const float a = act == 1 ? gelu_tanhf_(g) : siluf_(g);
-    reinterpret_cast<T*>(out_)[t * out_stride + out_off + i] = from_f32<T>(a * u);
+    T* out = reinterpret_cast<T*>(out_) + t * out_stride + out_off;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < I; i += gridDim.x * blockDim.x) {
+        const float g = to_f32<T>(in[gate_off + i]), u = to_f32<T>(in[up_off + i]);
+        const float a = act == 1 ? gelu_tanhf_(g) : siluf_(g);
+        out[i] = from_f32<T>(a * u);
+    }
 }
 
 MSGL_API int msgl_gated_act(const void* in, long long in_stride, int gate_off, int up_off, void* out, long long out_stride,
                             int out_off, int I, int act, int T, int dtype, cudaStream_t stream) {
     if (T <= 0 || I <= 0) return MSGL_OK;
     if (act != 0 && act != 1) return MSGL_ERR_SIZE;
-    const long long total = (long long)T * I;
-    const int blocks = (int)((total + 255) / 256);
+    if (T > 65535) return MSGL_ERR_SIZE;
+    const dim3 grid(min((I + 255) / 256, 64), T);
     if (dtype == MSGL_F32)
-        gated_act_kernel<float><<<blocks, 256, 0, stream>>>(in, in_stride, gate_off, up_off, out, out_stride, out_off, I, act, total);
+        gated_act_kernel<float><<<grid, 256, 0, stream>>>(in, in_stride, gate_off, up_off, out, out_stride, out_off, I, act);
     else if (dtype == MSGL_BF16)
-        gated_act_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(in, in_stride, gate_off, up_off, out, out_stride, out_off, I, act, total);
+        gated_act_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(in, in_stride, gate_off, up_off, out, out_stride, out_off, I, act);
+    else
+        return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// out[t, h, :] = x[t, h, :] * sigmoid(gate[t, h]) * c   (x dense [T, heads, d]; gate and out in packed rows)
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void head_gate_kernel(const T* __restrict__ x, const void* gate_, long long gate_stride, int gate_off, void* out_,
+                                 long long out_stride, int out_off, int heads, int d, float c) {
+    const long long t = blockIdx.x;
+    const T* g = gate_ ? reinterpret_cast<const T*>(gate_) + t * gate_stride + gate_off : nullptr;
+    T* o = reinterpret_cast<T*>(out_) + t * out_stride + out_off;
+    const T* xr = x + t * heads * d;
+    for (int i = threadIdx.x; i < heads * d; i += blockDim.x) {
+        const float f = g ? sigmoidf_(to_f32<T>(g[i / d])) * c : c;
+        o[i] = from_f32<T>(to_f32<T>(xr[i]) * f);
+    }
+}
+
+MSGL_API int msgl_head_gate(const void* x, const void* gate, long long gate_stride, int gate_off, void* out, long long out_stride,
+                            int out_off, int heads, int d, float c, int T, int dtype, cudaStream_t stream) {
+    if (T <= 0) return MSGL_OK;
+    if (heads <= 0 || d <= 0) return MSGL_ERR_SIZE;
+    if (dtype == MSGL_F32)
+        head_gate_kernel<float><<<T, 256, 0, stream>>>((const float*)x, gate, gate_stride, gate_off, out, out_stride, out_off, heads, d, c);
+    else if (dtype == MSGL_BF16)
+        head_gate_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16*)x, gate, gate_stride, gate_off, out, out_stride,
+                                                                out_off, heads, d, c);
     else
         return MSGL_ERR_DTYPE;
     return msgl_check_launch();

@@ -337,7 +337,8 @@ class ModelRunner:
         # blocks per kv head of a decode launch with an even cut of the keys: what the SMs hold at once; empty unless the
         # decode kernel of every group takes such a cut
         self._even_nb: List[int] = []
-        if self.dtype == torch.bfloat16 and self.mgr.groups and all(geom[2] for geom in self._group_geom):
+        if self.dtype == torch.bfloat16 and self.mgr.groups and all(geom[2] for geom in self._group_geom) and \
+                all(needs[cid].even_cut for g in self.mgr.groups for cid in g.cache_ids):
             ok = True
             for g, (n_kv, G, per_sm, _) in zip(self.mgr.groups, self._group_geom):
                 head_dim = needs[g.cache_ids[0]].head_dim

@@ -109,6 +109,7 @@ def _attn_lib(head_dim: int):
     if lib is None:
         lib = _build.attention_library(hd)
         lib.msgl_attention.argtypes = [c_void_p] * 10 + [c_int] * 9 + [c_float] + [c_int] * 6 + [c_void_p, c_void_p, c_int, c_void_p]
+        lib.msgl_attention_window.argtypes = [c_void_p] * 10 + [c_int] * 9 + [c_float] + [c_int] * 6 + [c_void_p, c_int, c_void_p, c_int, c_void_p]
         lib.msgl_attention_combine.argtypes = [c_void_p] * 5 + [c_int] * 5 + [c_void_p]
         lib.msgl_attention_tc.argtypes = [c_void_p] * 7 + [c_int] * 8 + [c_float] + [c_int] * 5 + [c_void_p, c_void_p]
         lib.msgl_attention_head_dim.restype = c_int
@@ -430,6 +431,12 @@ def decode_even_ok(head_dim: int, dtype: torch.dtype, group: int = 1) -> bool:
     return bool(lib.msgl_attention_decode_even_ok(int(group)))
 
 
+def window_bias_supported(head_dim: int, dtype: torch.dtype, group: int) -> bool:
+    """Whether `attention(keep_first=..., bias_log2=...)` takes this geometry: bfloat16, head sizes in steps of 32 (the mma
+    prefill kernel and the transposed decode kernel), up to 16 query heads a kv head."""
+    return mma_supported(head_dim, dtype) and head_dim % 32 == 0 and group <= 16
+
+
 def mma_supported(head_dim: int, dtype: torch.dtype) -> bool:
     return dtype == torch.bfloat16 and head_dim in _build.MMA_HEAD_DIMS
 
@@ -439,9 +446,12 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
               nsplit: Optional[torch.Tensor], part_o: Optional[torch.Tensor], part_ml: Optional[torch.Tensor],
               n_kv: int, page_size: int, window: int, max_split: int, scale: float, qlen_min: int, qlen_max: int,
               uniform_decode: bool, variant: int, grid_x: int, order: Optional[torch.Tensor] = None,
-              even: Optional[torch.Tensor] = None, even_nb: int = 0) -> None:
+              even: Optional[torch.Tensor] = None, even_nb: int = 0, keep_first: int = 0,
+              bias_log2: Optional[torch.Tensor] = None) -> None:
     """One launch of the paged attention kernel over the requests whose q_len lies in
-    [qlen_min, qlen_max]; see csrc/attention.cu for the meaning of every argument.  `order` (uniform decode only):
+    [qlen_min, qlen_max]; see csrc/attention.cu for the meaning of every argument.  keep_first: with a window, the first
+    keys of a request that stay visible whatever the window; bias_log2: float32 [heads, L], added to the scaled score in
+    log2 units by distance min(i - j, L - 1) (both: the bfloat16 mma kernels only, see `window_bias_supported`).  `order` (uniform decode only):
     int32 [B], a permutation of the requests; the launch's i-th block along x takes request order[i].  `even`: the even cut
     of a decode step's keys over `even_nb` blocks per kv head (engine/step.py: plan_even_cut) in place of `grid_x` blocks."""
     _need_cuda(q, out, k_cache, v_cache, q_start, kv_len, block_table, nsplit, part_o, part_ml, order, even)
@@ -455,6 +465,18 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
                             even.numel() >= even_cut_size(B, even_nb) and even_nb >= 1)
     if max_split > 1:
         assert part_o.numel() >= max_split * T * n_q * d and part_ml.numel() >= max_split * T * n_q * 2
+    if keep_first or bias_log2 is not None:
+        _need_cuda(bias_log2)
+        assert even is None, "the even cut of a decode step knows no kept tokens and no bias"
+        if bias_log2 is not None:
+            assert bias_log2.dtype == torch.float32 and bias_log2.dim() == 2 and bias_log2.shape[0] == n_q and bias_log2.is_contiguous()
+        code = _attn_lib(d).msgl_attention_window(
+            _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table),
+            _ptr(nsplit), _ptr(part_o), _ptr(part_ml), B, T, n_q, n_kv, d, page_size, block_table.stride(0), window,
+            max_split, float(scale), qlen_min, qlen_max, int(uniform_decode), variant, grid_x, _dt(q), _ptr(order),
+            int(keep_first), _ptr(bias_log2), bias_log2.shape[1] if bias_log2 is not None else 0, _stream())
+        _check(code, f"attention with kept tokens / bias (head size {d}, variant {variant})")
+        return
     code = _attn_lib(d).msgl_attention(
         _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table),
         _ptr(nsplit), _ptr(part_o), _ptr(part_ml), B, T, n_q, n_kv, d, page_size, block_table.stride(0), window,
@@ -647,6 +669,9 @@ def _mix_lib():
         lib.msgl_rms_gate.argtypes = [c_void_p, c_int, c_void_p, c_float, c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_float, c_int,
                                       c_int, c_void_p]
         lib.msgl_gated_act.argtypes = [c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        lib.msgl_head_gate.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]
+        lib.msgl_decay_attention_chunked.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int] + [c_void_p] * 6 + \
+            [c_int, c_int, c_int, c_void_p]
         _mixers = lib
     return _mixers
 
@@ -750,11 +775,34 @@ def window_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
     _check(code, f"window_attention (head size {d})")
 
 
+DECAY_CHUNK = 64                 # tokens per chunk of the chunked form of the decaying linear attention
+DECAY_CHUNKED_FROM = 16          # a step whose longest request brings this many tokens takes the chunked form
+
+
+def head_gate(x: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t, h, :] = x[t, h, :] * sigmoid(gate[t, h]) * scale; x [T, heads, d] contiguous, gate [T, heads] and out
+    [T, heads * d] views into packed rows."""
+    _need_cuda(x, gate, out)
+    T, H, d = x.shape
+    assert x.is_contiguous() and out.dtype == x.dtype
+    gs = 0
+    if gate is not None:
+        assert gate.dtype == x.dtype
+        gs = _rows_view(gate, H, "gate")
+    code = _mix_lib().msgl_head_gate(_ptr(x), _ptr(gate), gs, 0, _ptr(out), _rows_view(out, H * d, "out"), 0, H, d, float(scale), T,
+                                     _dt(x), _stream())
+    _check(code, "head_gate")
+
+
 def decay_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, heads: int, decay: torch.Tensor, state: torch.Tensor,
-                    q_start: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+                    q_start: torch.Tensor, slots: torch.Tensor, q_lens: Optional[Sequence[int]] = None,
+                    workspace=None) -> torch.Tensor:
     """Linear attention with a fixed decay per head over the step's tokens, continued from and written back to `state`
     [slots, heads, dk, dv] float32: S <- decay_h S + k v^T, o = S^T q with q, k, v = silu of the given projections
-    ([T, heads * dk], [T, heads * dk], [T, heads * dv]: views into one packed projection).  -> float32 [T, heads * dv]."""
+    ([T, heads * dk], [T, heads * dk], [T, heads * dv]: views into one packed projection).  -> float32 [T, heads * dv].
+    q_lens: the requests' numbers of tokens as the host knows them; when the longest has DECAY_CHUNKED_FROM or more, the
+    step is computed in chunks of DECAY_CHUNK tokens that run in parallel (the same sums in another order), else, and
+    without q_lens, every request's tokens are walked in order.  workspace: a parts.Workspace for the chunks' states."""
     _need_cuda(q, k, v, decay, state, q_start, slots)
     T = q.shape[0]
     dk, dv = q.shape[1] // heads, v.shape[1] // heads
@@ -766,6 +814,17 @@ def decay_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, heads:
     assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dk, dv)
     out = torch.empty((T, heads * dv), dtype=torch.float32, device=q.device)
     B = q_start.numel() - 1
+    if q_lens is not None and max(q_lens, default=0) >= DECAY_CHUNKED_FROM:
+        n_chunks = sum(-(-n // DECAY_CHUNK) for n in q_lens)
+        numel = n_chunks * heads * dk * dv
+        U = workspace.get("decay_chunk_states", numel, torch.float32) if workspace is not None else \
+            torch.empty(numel, dtype=torch.float32, device=q.device)
+        code = _mix_lib().msgl_decay_attention_chunked(_ptr(q), stride, 0, k_off, v_off, heads, dk, dv, _ptr(decay), _ptr(state),
+                                                       _ptr(q_start), _ptr(slots), _ptr(out), _ptr(U), n_chunks, B, _dt(q), _stream())
+        _check(code, f"decay_attention in chunks (key size {dk})")
+        global LAUNCHES
+        LAUNCHES += 2
+        return out
     code = _mix_lib().msgl_decay_attention(_ptr(q), stride, 0, k_off, v_off, heads, dk, dv, _ptr(decay), _ptr(state), _ptr(q_start),
                                            _ptr(slots), _ptr(out), B, _dt(q), _stream())
     _check(code, f"decay_attention (key size {dk})")

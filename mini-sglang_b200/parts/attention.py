@@ -100,45 +100,59 @@ class PagedAttention(Mixer):
         return ops.linear(out.view(ctx.T, self.n_q * self.d), self.o)
 
     def attend(self, q: torch.Tensor, out: torch.Tensor, ctx: StepContext, cache: KVCacheView) -> None:
-        g = cache.group
-        G = self.n_q // self.n_kv
-        window = int(self.window or 0)
-        max_split = g.max_split if g.nsplit is not None else 1
-        part_o = part_ml = None
-        if max_split > 1:
-            rows = max_split * ctx.T * self.n_q
-            part_o = ctx.workspace.get("attn_part_o", rows * self.d, torch.float32)
-            part_ml = ctx.workspace.get("attn_part_ml", rows * 2, torch.float32)
-        common = dict(q_start=ctx.q_start, kv_len=ctx.kv_len, block_table=g.block_table,
-                      nsplit=g.nsplit if max_split > 1 else None, part_o=part_o, part_ml=part_ml, n_kv=self.n_kv,
-                      page_size=cache.page_size, window=window, max_split=max_split, scale=self.scale,
-                      uniform_decode=ctx.uniform_decode, order=g.order if ctx.uniform_decode else None)
-        big = 1 << 30
-        if not self.use_mma:
-            qt = ops.attention_tile_tokens(ops.VARIANT_SIMT, G)
-            gx = ctx.B if ctx.uniform_decode else sum(-(-n // qt) for n in ctx.host_q_lens)
-            ops.attention(q, out, cache.k, cache.v, qlen_min=1, qlen_max=big, variant=ops.VARIANT_SIMT, grid_x=gx, **common)
+        paged_attend(q, out, ctx, cache, n_q=self.n_q, n_kv=self.n_kv, d=self.d, window=int(self.window or 0), scale=self.scale,
+                     use_mma=self.use_mma)
+
+
+def paged_attend(q: torch.Tensor, out: torch.Tensor, ctx: StepContext, cache: KVCacheView, *, n_q: int, n_kv: int, d: int,
+                 window: int, scale: float, use_mma: bool, keep_first: int = 0, bias_log2: Optional[torch.Tensor] = None) -> None:
+    """The attention launches of one step over a paged cache: requests that bring a few tokens through the decode kernel
+    with the step's kv splits, longer runs through the prefill kernels, the merge of the splits.  keep_first and bias_log2
+    (kept first tokens under a window, a bias by distance: `ops.attention`) are for mixers that have them; such launches
+    stay on the mma kernels."""
+    plain = keep_first == 0 and bias_log2 is None
+    if not plain and not use_mma:
+        raise ValueError("kept first tokens and a distance bias are taken by the bfloat16 mma kernels only")
+    extra = {} if plain else dict(keep_first=keep_first, bias_log2=bias_log2)
+    g = cache.group
+    G = n_q // n_kv
+    max_split = g.max_split if g.nsplit is not None else 1
+    part_o = part_ml = None
+    if max_split > 1:
+        rows = max_split * ctx.T * n_q
+        part_o = ctx.workspace.get("attn_part_o", rows * d, torch.float32)
+        part_ml = ctx.workspace.get("attn_part_ml", rows * 2, torch.float32)
+    common = dict(q_start=ctx.q_start, kv_len=ctx.kv_len, block_table=g.block_table,
+                  nsplit=g.nsplit if max_split > 1 else None, part_o=part_o, part_ml=part_ml, n_kv=n_kv,
+                  page_size=cache.page_size, window=window, max_split=max_split, scale=scale,
+                  uniform_decode=ctx.uniform_decode, order=g.order if ctx.uniform_decode else None, **extra)
+    big = 1 << 30
+    if not use_mma:
+        qt = ops.attention_tile_tokens(ops.VARIANT_SIMT, G)
+        gx = ctx.B if ctx.uniform_decode else sum(-(-n // qt) for n in ctx.host_q_lens)
+        ops.attention(q, out, cache.k, cache.v, qlen_min=1, qlen_max=big, variant=ops.VARIANT_SIMT, grid_x=gx, **common)
+    else:
+        qt_dec = ops.attention_tile_tokens(ops.VARIANT_MMA_DECODE, G, d)
+        qt_row = ops.attention_tile_tokens(ops.VARIANT_MMA_ROWS, G)
+        if ctx.uniform_decode:
+            even = dict(even=g.even, even_nb=g.even_nb) if plain else {}
+            ops.attention(q, out, cache.k, cache.v, qlen_min=1, qlen_max=1, variant=ops.VARIANT_MMA_DECODE,
+                          grid_x=ctx.B, **even, **common)
         else:
-            qt_dec = ops.attention_tile_tokens(ops.VARIANT_MMA_DECODE, G, self.d)
-            qt_row = ops.attention_tile_tokens(ops.VARIANT_MMA_ROWS, G)
-            if ctx.uniform_decode:
-                ops.attention(q, out, cache.k, cache.v, qlen_min=1, qlen_max=1, variant=ops.VARIANT_MMA_DECODE,
-                              grid_x=ctx.B, even=g.even, even_nb=g.even_nb, **common)
-            else:
-                n_dec = sum(1 for n in ctx.host_q_lens if n <= qt_dec)
-                n_row = sum(-(-n // qt_row) for n in ctx.host_q_lens if n > qt_dec)
-                if n_dec:
-                    ops.attention(q, out, cache.k, cache.v, qlen_min=1, qlen_max=qt_dec,
-                                  variant=ops.VARIANT_MMA_DECODE, grid_x=n_dec, **common)
-                # the tcgen05 kernels take whole key ranges: only if no longer request has kv splits
-                unsplit = max_split == 1 or (g.host_nsplit is not None and
-                                             all(ns == 1 for n, ns in zip(ctx.host_q_lens, g.host_nsplit) if n > qt_dec))
-                if n_row and unsplit and ops.tc_supported(self.d, q.dtype, G):
-                    ops.attention_tc(q, out, cache.k, cache.v, q_start=ctx.q_start, kv_len=ctx.kv_len,
-                                     block_table=g.block_table, n_kv=self.n_kv, page_size=cache.page_size, window=window,
-                                     scale=self.scale, qlen_min=qt_dec + 1, qlen_max=big, q_lens=ctx.host_q_lens)
-                elif n_row:
-                    ops.attention(q, out, cache.k, cache.v, qlen_min=qt_dec + 1, qlen_max=big,
-                                  variant=ops.VARIANT_MMA_ROWS, grid_x=n_row, **common)
-        if max_split > 1:
-            ops.attention_combine(part_o, part_ml, None if ctx.uniform_decode else ctx.token_req, g.nsplit, out, max_split)
+            n_dec = sum(1 for n in ctx.host_q_lens if n <= qt_dec)
+            n_row = sum(-(-n // qt_row) for n in ctx.host_q_lens if n > qt_dec)
+            if n_dec:
+                ops.attention(q, out, cache.k, cache.v, qlen_min=1, qlen_max=qt_dec,
+                              variant=ops.VARIANT_MMA_DECODE, grid_x=n_dec, **common)
+            # the tcgen05 kernels take whole key ranges: only if no longer request has kv splits
+            unsplit = max_split == 1 or (g.host_nsplit is not None and
+                                         all(ns == 1 for n, ns in zip(ctx.host_q_lens, g.host_nsplit) if n > qt_dec))
+            if n_row and plain and unsplit and ops.tc_supported(d, q.dtype, G):
+                ops.attention_tc(q, out, cache.k, cache.v, q_start=ctx.q_start, kv_len=ctx.kv_len,
+                                 block_table=g.block_table, n_kv=n_kv, page_size=cache.page_size, window=window,
+                                 scale=scale, qlen_min=qt_dec + 1, qlen_max=big, q_lens=ctx.host_q_lens)
+            elif n_row:
+                ops.attention(q, out, cache.k, cache.v, qlen_min=qt_dec + 1, qlen_max=big,
+                              variant=ops.VARIANT_MMA_ROWS, grid_x=n_row, **common)
+    if max_split > 1:
+        ops.attention_combine(part_o, part_ml, None if ctx.uniform_decode else ctx.token_req, g.nsplit, out, max_split)

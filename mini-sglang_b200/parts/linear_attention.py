@@ -64,7 +64,8 @@ class DecayLinearAttention(Mixer, Projected):
     def middle(self, proj, act, ctx, cache=None, writes_cache=True, out_scale=1.0):
         Nk, Nv = self.Nk, self.Nv
         o = ops.decay_attention(proj[:, :Nk], proj[:, Nk:2 * Nk], proj[:, 2 * Nk:2 * Nk + Nv], heads=self.heads, decay=self.decay,
-                                state=cache.state, q_start=ctx.q_start, slots=ctx.slots)
+                                state=cache.state, q_start=ctx.q_start, slots=ctx.slots,
+                                q_lens=None if ctx.uniform_decode else ctx.host_q_lens, workspace=ctx.workspace)
         ops.rms_gate(o, self.norm, self.eps, proj[:, 2 * Nk + Nv:2 * Nk + 2 * Nv], act, out_scale)
 
     def forward(self, x, ctx, cache, writes_cache: bool = True):

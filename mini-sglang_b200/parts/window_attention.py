@@ -8,6 +8,7 @@ import torch
 from .. import ops
 from ..cache.manager import PagedKVNeed, StateNeed
 from ..weights.loader import TensorDecl
+from .attention import paged_attend
 from .base import Mixer, Projected, register_mixer
 
 
@@ -62,7 +63,10 @@ class ConvWindowAttention(Mixer, Projected):
                  "bias": "distance_bias", "gate": "gate", "out": "out"}
         names.update(s.get("names") or {})
         self.names = {k: self.name(v) for k, v in names.items()}
-        self.w_in = self.w_out = self.q_taps = self.k_taps = self.q_norm = self.k_norm = self.bias = None
+        # bfloat16 at head sizes the mma kernels of csrc/attention.cu take: those, with the step's kv splits; otherwise (true
+        # float32, other head sizes) the float32-arithmetic kernel of csrc/mixers.cu, which takes every request whole
+        self.use_mma = ops.window_bias_supported(self.d, env.dtype, self.n_q // self.n_kv)
+        self.w_in = self.w_out = self.q_taps = self.k_taps = self.q_norm = self.k_norm = self.bias = self.bias_log2 = None
 
     # -- weights -----------------------------------------------------------------------
     def tensors(self) -> Dict[str, TensorDecl]:
@@ -89,6 +93,7 @@ class ConvWindowAttention(Mixer, Projected):
         n_dist = int(math.ceil(self.bias_far)) + 1 if rows > 1 else 1
         idx = distance_buckets(rows, self.bias_far, n_dist).to(table.device)
         self.bias = table[idx].t().contiguous()                         # [heads, distances]
+        self.bias_log2 = (self.bias * math.log2(math.e)).contiguous() if self.use_mma else None
 
     def in_weight(self):
         return self.w_in
@@ -97,7 +102,8 @@ class ConvWindowAttention(Mixer, Projected):
         return self.w_out
 
     def cache_need(self):
-        return (PagedKVNeed(self.n_kv, self.d, self.window, q_heads=self.n_q, keep_first=self.keep_first, library="mixers"),
+        return (PagedKVNeed(self.n_kv, self.d, self.window, q_heads=self.n_q, keep_first=self.keep_first,
+                            library="attention" if self.use_mma else "mixers", even_cut=False),
                 StateNeed((self.taps - 1, self.Cq + self.Ck), "compute"))
 
     # -- compute -----------------------------------------------------------------------
@@ -109,11 +115,19 @@ class ConvWindowAttention(Mixer, Projected):
                                   token_req=ctx.token_req, q_start=ctx.q_start, slots=ctx.slots,
                                   out_loc=kv.group.out_loc if writes_cache else None, k_cache=kv.k if writes_cache else None,
                                   v_cache=kv.v if writes_cache else None, page_size=kv.page_size)
+        gate = proj[:, Cq + Ck:Cq + Ck + self.n_q]
+        if self.use_mma:
+            q3 = q.view(ctx.T, self.n_q, self.d)
+            o = torch.empty_like(q3)
+            paged_attend(q3, o, ctx, kv, n_q=self.n_q, n_kv=self.n_kv, d=self.d, window=int(self.window or 0), scale=self.scale,
+                         use_mma=True, keep_first=self.keep_first, bias_log2=self.bias_log2)
+            ops.head_gate(o, gate, act, out_scale)
+            return
         ops.window_attention(q.view(ctx.T, self.n_q, self.d), act, kv.k, kv.v, q_start=ctx.q_start, kv_len=ctx.kv_len,
                              block_table=kv.group.block_table, n_kv=self.n_kv, page_size=kv.page_size,
                              window=int(self.window or 0), keep_first=self.keep_first, scale=self.scale,
-                             q_lens=None if ctx.uniform_decode else ctx.host_q_lens, bias=self.bias,
-                             gate=proj[:, Cq + Ck:Cq + Ck + self.n_q], out_scale=out_scale)
+                             q_lens=None if ctx.uniform_decode else ctx.host_q_lens, bias=self.bias, gate=gate,
+                             out_scale=out_scale)
 
     def forward(self, x, ctx, cache, writes_cache: bool = True):
         return self.forward_projected(x, ctx, cache, writes_cache)

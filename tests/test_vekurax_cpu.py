@@ -61,7 +61,7 @@ def test_cache_needs_of_a_pair_of_mixers():
     model = DecoderModel(arch.build_spec(arch.config_cls.from_dict(raw)), BuildEnv(torch.bfloat16, torch.device("cpu")))
     needs = model.cache_needs()
     assert sorted(needs) == [(c, k) for c in range(4) for k in range(3)]
-    assert needs[(0, 0)] == PagedKVNeed(3, 24, 9, q_heads=6, keep_first=3, library="mixers")
+    assert needs[(0, 0)] == PagedKVNeed(3, 24, 9, q_heads=6, keep_first=3, library="mixers", even_cut=False)
     assert needs[(1, 0)].window == 5 and needs[(1, 0)].keep_first == 0
     assert needs[(0, 1)] == StateNeed((2, 6 * 24 + 3 * 24), "compute") and needs[(0, 2)] == StateNeed((3, 12, 20), "float32")
     mgr = CacheManager(needs, page_size=4, num_pages=40, max_reqs=3, max_context_len=512)

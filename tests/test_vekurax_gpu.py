@@ -228,15 +228,40 @@ def _window_case(dtype, *, H, G, d, P, window, keep_first, rows, far, ctx, n_new
     assert torch.isfinite(got).all()
     tol = dict(rtol=1e-4, atol=1e-4) if dtype == "float32" else dict(rtol=3e-2, atol=3e-2)
     torch.testing.assert_close(got, want.float(), **tol)
+    if ops.window_bias_supported(d, dt, H // G):
+        # the same through the mma kernels of the paged attention launch: the prefill kernel, and for a few tokens the decode
+        # kernel, whole and with the keys cut into pieces (the kept tokens then ride with the first piece)
+        bias_log2 = (bias * math.log2(math.e)).contiguous().cuda()
+        ungated = (want / torch.sigmoid(gate.double())[:, :, None] / 1.25).float()
+        qd, kd, vd = q.to(dt).cuda(), kc.cuda(), vc.cuda()
+        common = dict(q_start=torch.tensor([0, n_new], dtype=torch.int32).cuda(), kv_len=torch.tensor([L], dtype=torch.int32).cuda(),
+                      block_table=perm.to(torch.int32)[None].contiguous().cuda(), n_kv=G, page_size=P, window=window, scale=scale,
+                      uniform_decode=n_new == 1, keep_first=keep_first, bias_log2=bias_log2)
+        runs = [(ops.VARIANT_MMA_ROWS, 1)]
+        if n_new <= ops.attention_tile_tokens(ops.VARIANT_MMA_DECODE, H // G, d):
+            runs += [(ops.VARIANT_MMA_DECODE, 1), (ops.VARIANT_MMA_DECODE, 3)]
+        for variant, ns in runs:
+            o = torch.full((n_new, H, d), float("nan"), dtype=dt).cuda()
+            part_o = torch.empty(ns * n_new * H * d, dtype=torch.float32).cuda() if ns > 1 else None
+            part_ml = torch.empty(ns * n_new * H * 2, dtype=torch.float32).cuda() if ns > 1 else None
+            nsplit = torch.tensor([ns], dtype=torch.int32).cuda() if ns > 1 else None
+            qt = ops.attention_tile_tokens(variant, H // G, d)
+            ops.attention(qd, o, kd, vd, nsplit=nsplit, part_o=part_o, part_ml=part_ml, max_split=ns, qlen_min=1, qlen_max=1 << 30,
+                          variant=variant, grid_x=-(-n_new // qt), **common)
+            if ns > 1:
+                ops.attention_combine(part_o, part_ml, None if n_new == 1 else torch.zeros(n_new, dtype=torch.int32).cuda(), nsplit, o, ns)
+            assert torch.isfinite(o).all(), (variant, ns)
+            torch.testing.assert_close(o.float().cpu(), ungated, rtol=3e-2, atol=3e-2, msg=lambda m: f"variant {variant}, {ns} pieces: {m}")
     return want
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("n_new", [1, 13])
-def test_window_attention_sees_exactly_the_window_and_the_kept_tokens(dtype, n_new):
+@pytest.mark.parametrize("d", [24, 32])
+def test_window_attention_sees_exactly_the_window_and_the_kept_tokens(dtype, n_new, d):
     """A key that would take all the weight sits just inside the window, just outside it, on the last kept first token, on
     the first token that is not kept, far behind, and at page borders; for a prompt's portion and for a decoded token."""
-    geo = dict(H=6, G=3, d=24, P=4, window=9, keep_first=3, rows=10, far=37, ctx=150)
+    geo = dict(H=6, G=3, d=d, P=4, window=9, keep_first=3, rows=10, far=37, ctx=150)
     wants = {}
     for name, spike in (("inside", (8,)), ("outside", (9,)), ("far", (140,)), ("kept", ("abs", 2)), ("not kept", ("abs", 3)),
                         ("first", ("abs", 0)), ("page border", (4,)), ("self", (0,)), ("none", ("abs", -1))):
@@ -260,6 +285,10 @@ def test_window_attention_other_geometries(dtype):
     # decoding the second token of a sequence; decoding with the window's far edge on a page border
     _window_case(dtype, H=4, G=2, d=32, P=4, window=8, keep_first=2, rows=8, far=64, ctx=1, n_new=1, spike_at=(1,), seed=5)
     _window_case(dtype, H=4, G=2, d=32, P=4, window=8, keep_first=2, rows=8, far=64, ctx=31, n_new=1, spike_at=(7,), seed=6)
+    # a window of several key tiles with kept tokens far before it: a decoded token, a short run and a long portion
+    for n_new in (1, 3, 90):
+        _window_case(dtype, H=8, G=2, d=96, P=16, window=200, keep_first=70, rows=32, far=240, ctx=700, n_new=n_new, spike_at=("abs", 69), seed=7)
+        _window_case(dtype, H=8, G=2, d=96, P=16, window=200, keep_first=70, rows=32, far=240, ctx=700, n_new=n_new, spike_at=(199,), seed=8)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -360,9 +360,25 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
         bias_hi = p.bias + (size_t)min(kvh * G + chunk * R + (r_hi - (r_hi / Gc) * Gc), p.n_q - 1) * p.bias_len;
     }
     const float sc_exp = (EXT && p.bias) ? 1.f : sc;          // with a bias the scores are brought to log2 units where it is added
+    // The bias of a key tile through shared memory: a row's distances to the tile's 64 keys are consecutive, so per head of
+    // the block the tile needs QT + 63 consecutive table entries; entry j of a head stands for distance dmin + j with
+    // dmin = p_min - (last key of the tile), and row (token tl, head hl) reads key kk of the tile at tl + 63 - kk.
+    constexpr int BS_HEADS = 8, BS_LD = 136;
+    __shared__ float bias_s[EXT ? BS_HEADS * BS_LD : 1];
+    const bool bias_staged = EXT && p.bias != nullptr && Gc <= BS_HEADS;
+    const float* bs_lo = bias_s + (r_lo - (r_lo / Gc) * Gc) * BS_LD + r_lo / Gc + (MMA_KT - 1) - (lane & 3) * 2;
+    const float* bs_hi = bias_s + (r_hi - (r_hi / Gc) * Gc) * BS_LD + r_hi / Gc + (MMA_KT - 1) - (lane & 3) * 2;
 
     for (int it = 0; it < n_tiles; ++it) {
         const int kt = tile_of(it);
+        if (bias_staged) {       // read between the barrier below and the one that ends the iteration
+            const int dmin = p_min - (kt * MMA_KT + MMA_KT - 1), span = QT + MMA_KT - 1;
+            for (int idx = tid; idx < Gc * span; idx += MMA_THREADS) {
+                const int hl = idx / span, j = idx - hl * span;
+                const int head = min(kvh * G + chunk * R + hl, p.n_q - 1);
+                bias_s[hl * BS_LD + j] = p.bias[(size_t)head * p.bias_len + min(max(dmin + j, 0), p.bias_len - 1)];
+            }
+        }
         if (it + 1 < n_tiles) {
             load_kv((it + 1) & 1, tile_of(it + 1), pg_next);
             cp_async_commit();
@@ -413,7 +429,9 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
                         if (p.window > 0) ok = ok && (key > pos - p.window);
                     }
                     if (!ok) v = -INFINITY;
-                    else if (EXT && p.bias) v = fmaf(v, sc, ((e < 2) ? bias_lo : bias_hi)[min(max(pos - key, 0), p.bias_len - 1)]);
+                    else if (EXT && p.bias)
+                        v = fmaf(v, sc, bias_staged ? ((e < 2) ? bs_lo : bs_hi)[-(nb * 8 + (e & 1))]
+                                                    : ((e < 2) ? bias_lo : bias_hi)[min(max(pos - key, 0), p.bias_len - 1)]);
                     s[nb][e] = v;
                 }
                 if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);

@@ -28,22 +28,57 @@ __device__ __forceinline__ float gelu_tanhf_(float z) {
     return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+
+// two neighbouring elements at once (V = 2) where pointers, strides and widths are even, else one (V = 1)
+template <int V> __device__ __forceinline__ void ld_v(const float* p, float (&o)[2]) {
+    if (V == 2) { const float2 t = *reinterpret_cast<const float2*>(p); o[0] = t.x; o[1] = t.y; } else { o[0] = p[0]; o[1] = 0.f; }
+}
+template <int V> __device__ __forceinline__ void ld_v(const __nv_bfloat16* p, float (&o)[2]) {
+    if (V == 2) { const __nv_bfloat162 t = *reinterpret_cast<const __nv_bfloat162*>(p); o[0] = __low2float(t); o[1] = __high2float(t); }
+    else { o[0] = __bfloat162float(p[0]); o[1] = 0.f; }
+}
+template <int V> __device__ __forceinline__ void st_v(float* p, const float (&o)[2]) {
+    if (V == 2) *reinterpret_cast<float2*>(p) = make_float2(o[0], o[1]); else p[0] = o[0];
+}
+template <int V> __device__ __forceinline__ void st_v(__nv_bfloat16* p, const float (&o)[2]) {
+    if (V == 2) *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(o[0], o[1]); else p[0] = __float2bfloat16_rn(o[0]);
+}
+static inline bool even_all(long long a, long long b = 0, long long c = 0, long long d = 0, long long e = 0, long long f = 0) {
+    return ((a | b | c | d | e | f) & 1) == 0;
+}
+static inline bool aligned_to(const void* p, size_t n) { return p == nullptr || ((uintptr_t)p % n) == 0; }
+
 // ---------------------------------------------------------------------------------------
 // Dynamic Tanh norm
 // ---------------------------------------------------------------------------------------
-template <typename T, typename X>
+template <typename T, typename X, int V>
 __global__ void dyntanh_kernel(const X* __restrict__ x, const float* __restrict__ res_in, float* __restrict__ res_out,
                                const int* __restrict__ row_idx, const float* __restrict__ w, const float* __restrict__ b,
                                float alpha, T* __restrict__ y, int H) {
     const int i = blockIdx.x;
     const size_t r = row_idx ? (size_t)row_idx[i] : (size_t)i;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        float v = 0.f;
-        if (res_in) v = res_in[r * H + c];
-        if (x) v += to_f32<X>(x[r * H + c]);
-        if (res_out) res_out[r * H + c] = v;
-        y[(size_t)i * H + c] = from_f32<T>(tanhf(alpha * v) * w[c] + b[c]);
+    for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * V; c < H; c += gridDim.y * blockDim.x * V) {
+        float v[2] = {0.f, 0.f}, xv[2] = {0.f, 0.f}, wv[2], bv[2], o[2];
+        if (res_in) ld_v<V>(res_in + r * H + c, v);
+        if (x) { ld_v<V>(x + r * H + c, xv); v[0] += xv[0]; v[1] += xv[1]; }
+        if (res_out) st_v<V>(res_out + r * H + c, v);
+        ld_v<V>(w + c, wv);
+        ld_v<V>(b + c, bv);
+        o[0] = tanhf(alpha * v[0]) * wv[0] + bv[0];
+        o[1] = V == 2 ? tanhf(alpha * v[1]) * wv[1] + bv[1] : 0.f;
+        st_v<V>(y + (size_t)i * H + c, o);
     }
+}
+
+template <typename T, typename X>
+static void dyntanh_launch(const void* x, const float* res_in, float* res_out, const int* row_idx, const float* w, const float* b,
+                           float alpha, void* y, int rows, int H, cudaStream_t stream) {
+    const bool v2 = even_all(H) && aligned_to(x, 2 * sizeof(X)) && aligned_to(res_in, 8) && aligned_to(res_out, 8) && aligned_to(w, 8) &&
+                    aligned_to(b, 8) && aligned_to(y, 2 * sizeof(T));
+    const int per = v2 ? 2 : 1;
+    const dim3 grid(rows, max(1, min((H + 128 * per - 1) / (128 * per), 32)));
+    if (v2) dyntanh_kernel<T, X, 2><<<grid, 128, 0, stream>>>((const X*)x, res_in, res_out, row_idx, w, b, alpha, (T*)y, H);
+    else dyntanh_kernel<T, X, 1><<<grid, 128, 0, stream>>>((const X*)x, res_in, res_out, row_idx, w, b, alpha, (T*)y, H);
 }
 
 MSGL_API int msgl_dyntanh(const void* x, int x_is_f32, const float* res_in, float* res_out, const int* row_idx,
@@ -51,17 +86,10 @@ MSGL_API int msgl_dyntanh(const void* x, int x_is_f32, const float* res_in, floa
                           cudaStream_t stream) {
     if (rows <= 0) return MSGL_OK;
     if (H <= 0) return MSGL_ERR_SIZE;
-    const int threads = H >= 1024 ? 256 : 128;
-    if (dtype == MSGL_F32)
-        dyntanh_kernel<float, float><<<rows, threads, 0, stream>>>((const float*)x, res_in, res_out, row_idx, w, b, alpha, (float*)y, H);
-    else if (dtype == MSGL_BF16 && x_is_f32)
-        dyntanh_kernel<__nv_bfloat16, float><<<rows, threads, 0, stream>>>((const float*)x, res_in, res_out, row_idx, w, b, alpha,
-                                                                             (__nv_bfloat16*)y, H);
-    else if (dtype == MSGL_BF16)
-        dyntanh_kernel<__nv_bfloat16, __nv_bfloat16><<<rows, threads, 0, stream>>>((const __nv_bfloat16*)x, res_in, res_out, row_idx, w, b,
-                                                                                     alpha, (__nv_bfloat16*)y, H);
-    else
-        return MSGL_ERR_DTYPE;
+    if (dtype == MSGL_F32) dyntanh_launch<float, float>(x, res_in, res_out, row_idx, w, b, alpha, y, rows, H, stream);
+    else if (dtype == MSGL_BF16 && x_is_f32) dyntanh_launch<__nv_bfloat16, float>(x, res_in, res_out, row_idx, w, b, alpha, y, rows, H, stream);
+    else if (dtype == MSGL_BF16) dyntanh_launch<__nv_bfloat16, __nv_bfloat16>(x, res_in, res_out, row_idx, w, b, alpha, y, rows, H, stream);
+    else return MSGL_ERR_DTYPE;
     return msgl_check_launch();
 }
 
@@ -87,10 +115,10 @@ struct ConvNormParams {
     int T;
 };
 
-template <typename T>
-__global__ void conv_norm_kvwrite_kernel(const ConvNormParams p) {
+template <typename T, int V, int KMAX /* most taps: 4 or MIX_MAX_TAPS */>
+__global__ void __launch_bounds__(KMAX <= 4 ? 1024 : 256) conv_norm_kvwrite_kernel(const ConvNormParams p) {
     extern __shared__ float ybuf[];                  // [Cq + Ck]
-    __shared__ float red[32];
+    __shared__ float red[64];
     const int t = blockIdx.x;
     const int r = p.token_req[t];
     const int t0 = p.q_start[r];
@@ -100,42 +128,67 @@ __global__ void conv_norm_kvwrite_kernel(const ConvNormParams p) {
     const T* proj = reinterpret_cast<const T*>(p.proj);
     const T* st = reinterpret_cast<const T*>(p.state) + (size_t)slot * (K - 1) * C;
     float ssq_q = 0.f, ssq_k = 0.f;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    for (int c = threadIdx.x * V; c < C; c += blockDim.x * V) {
         const bool is_q = c < p.Cq;
         const int cc = is_q ? c : c - p.Cq;
         const float* w = (is_q ? p.wq_conv : p.wk_conv) + (size_t)cc * K;
         const int col = is_q ? p.q_off + cc : p.k_off + cc;
-        float acc = 0.f;
-        for (int j = 0; j < K; ++j) {
-            const int idx = i - (K - 1) + j;         // relative to the step's first token of this request
-            float u;
-            if (idx >= 0) u = to_f32<T>(proj[(size_t)(t0 + idx) * p.stride + col]);
-            else u = to_f32<T>(st[(size_t)(K - 1 + idx) * C + c]);
-            acc = fmaf(w[j], u, acc);
+        // every input of the taps first, then the sums: the loads are in flight together
+        float u[KMAX][2];
+#pragma unroll
+        for (int j = 0; j < KMAX; ++j) {
+            if (j < K) {
+                const int idx = i - (K - 1) + j;     // relative to the step's first token of this request
+                if (idx >= 0) ld_v<V>(proj + (size_t)(t0 + idx) * p.stride + col, u[j]);
+                else ld_v<V>(st + (size_t)(K - 1 + idx) * C + c, u[j]);
+            }
         }
-        const float y = to_f32<T>(from_f32<T>(acc));  // as it leaves the convolution, in the activation type
-        ybuf[c] = y;
-        if (is_q) ssq_q += y * y; else ssq_k += y * y;
+        float acc[2] = {0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < KMAX; ++j) {
+            if (j < K) {
+                acc[0] = fmaf(w[j], u[j][0], acc[0]);
+                if (V == 2) acc[1] = fmaf(w[K + j], u[j][1], acc[1]);
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            const float y = to_f32<T>(from_f32<T>(acc[v]));   // as it leaves the convolution, in the activation type
+            ybuf[c + v] = y;
+            if (is_q) ssq_q += y * y; else ssq_k += y * y;
+        }
     }
-    ssq_q = block_sum(ssq_q, red);
-    ssq_k = block_sum(ssq_k, red);
+    // both sums over the block at once
+    {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        ssq_q = warp_sum(ssq_q);
+        ssq_k = warp_sum(ssq_k);
+        if (lane == 0) { red[warp] = ssq_q; red[32 + warp] = ssq_k; }
+        __syncthreads();
+        const int nwarps = (blockDim.x + 31) >> 5;
+        ssq_q = warp_sum(lane < nwarps ? red[lane] : 0.f);
+        ssq_k = warp_sum(lane < nwarps ? red[32 + lane] : 0.f);
+    }
     const float rq = 1.f / sqrtf(ssq_q / (float)p.Cq + p.eps), rk = 1.f / sqrtf(ssq_k / (float)p.Ck + p.eps);
-    __syncthreads();
     T* qo = reinterpret_cast<T*>(p.q_out) + (size_t)t * p.Cq;
     const int loc = p.out_loc ? p.out_loc[t] : 0;
     const int page = loc / p.page_size, ps = loc - page * p.page_size;
     T* kc = reinterpret_cast<T*>(p.k_cache);
     T* vc = reinterpret_cast<T*>(p.v_cache);
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        const float y = ybuf[c];
+    for (int c = threadIdx.x * V; c < C; c += blockDim.x * V) {      // a thread reads back what it wrote itself
+        float y[2] = {ybuf[c], V == 2 ? ybuf[c + 1] : 0.f}, o[2], wn[2];
         if (c < p.Cq) {
-            qo[c] = from_f32<T>(y * rq * p.wq_norm[c]);
+            ld_v<V>(p.wq_norm + c, wn);
+            o[0] = y[0] * rq * wn[0]; o[1] = y[1] * rq * wn[1];
+            st_v<V>(qo + c, o);
         } else if (kc) {
             const int cc = c - p.Cq;
             const int g = cc / p.d, e = cc - g * p.d;
             const size_t a = (((size_t)page * p.n_kv + g) * p.page_size + ps) * p.d + e;
-            kc[a] = from_f32<T>(y * rk * p.wk_norm[cc]);
-            vc[a] = from_f32<T>(y);
+            ld_v<V>(p.wk_norm + cc, wn);
+            o[0] = y[0] * rk * wn[0]; o[1] = y[1] * rk * wn[1];
+            st_v<V>(kc + a, o);
+            st_v<V>(vc + a, y);
         }
     }
 }
@@ -179,28 +232,37 @@ MSGL_API int msgl_conv_norm_kvwrite(const void* proj, long long stride, int q_of
     p.k_cache = k_cache; p.v_cache = v_cache; p.page_size = page_size; p.T = T;
     const size_t smem = (size_t)(Cq + Ck) * sizeof(float);
     if (smem > 200 * 1024) return MSGL_ERR_SIZE;
-    const int threads = (Cq + Ck) >= 2048 ? 512 : 256;
-    static MsglOncePerDevice once_f, once_b;
-    if (dtype == MSGL_F32) {
-        if (smem > 48 * 1024 && once_f.due()) {
-            cudaFuncSetAttribute(conv_norm_kvwrite_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-            once_f.mark();
-        }
-        conv_norm_kvwrite_kernel<float><<<T, threads, smem, stream>>>(p);
-        if (taps > 1)
-            conv_state_update_kernel<float><<<dim3(B, (Cq + Ck + 255) / 256), 256, 0, stream>>>(proj, stride, q_off, k_off, Cq, Ck, taps,
-                                                                                                 state, q_start, slots);
-    } else if (dtype == MSGL_BF16) {
-        if (smem > 48 * 1024 && once_b.due()) {
-            cudaFuncSetAttribute(conv_norm_kvwrite_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-            once_b.mark();
-        }
-        conv_norm_kvwrite_kernel<__nv_bfloat16><<<T, threads, smem, stream>>>(p);
-        if (taps > 1)
-            conv_state_update_kernel<__nv_bfloat16><<<dim3(B, (Cq + Ck + 255) / 256), 256, 0, stream>>>(proj, stride, q_off, k_off, Cq, Ck,
-                                                                                                         taps, state, q_start, slots);
-    } else {
-        return MSGL_ERR_DTYPE;
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    const size_t item = dtype == MSGL_F32 ? 4 : 2;
+    // pairs of channels where nothing is odd: widths, head size, offsets, strides, pointers
+    const bool v2 = even_all(Cq, Ck, d, q_off, k_off, stride) && aligned_to(proj, 2 * item) && aligned_to(state, 2 * item) &&
+                    aligned_to(q_out, 2 * item) && aligned_to(k_cache, 2 * item) && aligned_to(v_cache, 2 * item) &&
+                    aligned_to(wq_norm, 8) && aligned_to(wk_norm, 8);
+    const int per = v2 ? 2 : 1;
+    const int C = Cq + Ck;
+    const bool few = taps <= 4;
+    const int threads = !few ? 256 : (C / per >= 2048 ? 1024 : (C / per >= 512 ? 512 : 256));
+#define CONV_LAUNCH(T, V, KM)                                                                                         \
+    do {                                                                                                              \
+        static MsglOncePerDevice once;                                                                                \
+        if (smem > 48 * 1024 && once.due()) {                                                                         \
+            cudaFuncSetAttribute(conv_norm_kvwrite_kernel<T, V, KM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            once.mark();                                                                                              \
+        }                                                                                                             \
+        conv_norm_kvwrite_kernel<T, V, KM><<<T_, threads, smem, stream>>>(p);                                         \
+    } while (0)
+#define CONV_LAUNCH_K(T, V) do { if (few) CONV_LAUNCH(T, V, 4); else CONV_LAUNCH(T, V, MIX_MAX_TAPS); } while (0)
+    const int T_ = T;
+    if (dtype == MSGL_F32) { if (v2) CONV_LAUNCH_K(float, 2); else CONV_LAUNCH_K(float, 1); }
+    else { if (v2) CONV_LAUNCH_K(__nv_bfloat16, 2); else CONV_LAUNCH_K(__nv_bfloat16, 1); }
+#undef CONV_LAUNCH_K
+#undef CONV_LAUNCH
+    if (taps > 1) {
+        const dim3 grid(B, (C + 255) / 256);
+        if (dtype == MSGL_F32)
+            conv_state_update_kernel<float><<<grid, 256, 0, stream>>>(proj, stride, q_off, k_off, Cq, Ck, taps, state, q_start, slots);
+        else
+            conv_state_update_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(proj, stride, q_off, k_off, Cq, Ck, taps, state, q_start, slots);
     }
     return msgl_check_launch();
 }
@@ -737,22 +799,30 @@ MSGL_API int msgl_decay_attention_chunked(const void* proj, long long stride, in
 // ---------------------------------------------------------------------------------------
 // y = x / sqrt(mean(x^2) + eps) * w * sigmoid(gate) * c   (x float32 [T, N]; gate and y in packed rows)
 // ---------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, int V>
 __global__ void rms_gate_kernel(const float* __restrict__ x, int N, const float* __restrict__ w, float eps, const void* gate_,
                                 long long gate_stride, int gate_off, void* out_, long long out_stride, int out_off, float c) {
     __shared__ float red[32];
     const int t = blockIdx.x;
     const float* xr = x + (size_t)t * N;
     float ssq = 0.f;
-    for (int i = threadIdx.x; i < N; i += blockDim.x) ssq += xr[i] * xr[i];
+    for (int i = threadIdx.x * V; i < N; i += blockDim.x * V) {
+        float v[2];
+        ld_v<V>(xr + i, v);
+        ssq += v[0] * v[0] + v[1] * v[1];
+    }
     ssq = block_sum(ssq, red);
     const float rs = 1.f / sqrtf(ssq / (float)N + eps);
     const T* g = gate_ ? reinterpret_cast<const T*>(gate_) + (size_t)t * gate_stride + gate_off : nullptr;
     T* o = reinterpret_cast<T*>(out_) + (size_t)t * out_stride + out_off;
-    for (int i = threadIdx.x; i < N; i += blockDim.x) {
-        float y = xr[i] * rs * w[i];
-        if (g) y *= sigmoidf_(to_f32<T>(g[i]));
-        o[i] = from_f32<T>(y * c);
+    for (int i = threadIdx.x * V; i < N; i += blockDim.x * V) {
+        float v[2], wv[2], gv[2] = {0.f, 0.f}, y[2];
+        ld_v<V>(xr + i, v);
+        ld_v<V>(w + i, wv);
+        if (g) ld_v<V>(g + i, gv);
+        y[0] = v[0] * rs * wv[0] * (g ? sigmoidf_(gv[0]) : 1.f) * c;
+        y[1] = v[1] * rs * wv[1] * (g ? sigmoidf_(gv[1]) : 1.f) * c;
+        st_v<V>(o + i, y);
     }
 }
 
@@ -760,29 +830,37 @@ MSGL_API int msgl_rms_gate(const float* x, int N, const float* w, float eps, con
                            void* out, long long out_stride, int out_off, float c, int T, int dtype, cudaStream_t stream) {
     if (T <= 0) return MSGL_OK;
     if (N <= 0) return MSGL_ERR_SIZE;
-    const int threads = N >= 1024 ? 256 : 128;
-    if (dtype == MSGL_F32)
-        rms_gate_kernel<float><<<T, threads, 0, stream>>>(x, N, w, eps, gate, gate_stride, gate_off, out, out_stride, out_off, c);
-    else if (dtype == MSGL_BF16)
-        rms_gate_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(x, N, w, eps, gate, gate_stride, gate_off, out, out_stride, out_off, c);
-    else
-        return MSGL_ERR_DTYPE;
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    const size_t item = dtype == MSGL_F32 ? 4 : 2;
+    const bool v2 = even_all(N, gate_stride, gate_off, out_stride, out_off) && aligned_to(x, 8) && aligned_to(w, 8) &&
+                    aligned_to(gate, 2 * item) && aligned_to(out, 2 * item);
+    const int threads = N >= 2048 ? 512 : (N >= 512 ? 256 : 128);
+    if (dtype == MSGL_F32) {
+        if (v2) rms_gate_kernel<float, 2><<<T, threads, 0, stream>>>(x, N, w, eps, gate, gate_stride, gate_off, out, out_stride, out_off, c);
+        else rms_gate_kernel<float, 1><<<T, threads, 0, stream>>>(x, N, w, eps, gate, gate_stride, gate_off, out, out_stride, out_off, c);
+    } else {
+        if (v2) rms_gate_kernel<__nv_bfloat16, 2><<<T, threads, 0, stream>>>(x, N, w, eps, gate, gate_stride, gate_off, out, out_stride, out_off, c);
+        else rms_gate_kernel<__nv_bfloat16, 1><<<T, threads, 0, stream>>>(x, N, w, eps, gate, gate_stride, gate_off, out, out_stride, out_off, c);
+    }
     return msgl_check_launch();
 }
 
 // ---------------------------------------------------------------------------------------
 // out = act(gate) * up; act 0 = silu, 1 = gelu (tanh form)
 // ---------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, int V>
 __global__ void gated_act_kernel(const void* in_, long long in_stride, int gate_off, int up_off, void* out_, long long out_stride,
                                  int out_off, int I, int act) {
-    const long long t = blockIdx.y;
+    const long long t = blockIdx.x;
     const T* in = reinterpret_cast<const T*>(in_) + t * in_stride;
     T* out = reinterpret_cast<T*>(out_) + t * out_stride + out_off;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < I; i += gridDim.x * blockDim.x) {
-        const float g = to_f32<T>(in[gate_off + i]), u = to_f32<T>(in[up_off + i]);
-        const float a = act == 1 ? gelu_tanhf_(g) : siluf_(g);
-        out[i] = from_f32<T>(a * u);
+    for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * V; i < I; i += gridDim.y * blockDim.x * V) {
+        float g[2], u[2], o[2];
+        ld_v<V>(in + gate_off + i, g);
+        ld_v<V>(in + up_off + i, u);
+        o[0] = (act == 1 ? gelu_tanhf_(g[0]) : siluf_(g[0])) * u[0];
+        o[1] = V == 2 ? (act == 1 ? gelu_tanhf_(g[1]) : siluf_(g[1])) * u[1] : 0.f;
+        st_v<V>(out + i, o);
     }
 }
 
@@ -790,30 +868,37 @@ MSGL_API int msgl_gated_act(const void* in, long long in_stride, int gate_off, i
                             int out_off, int I, int act, int T, int dtype, cudaStream_t stream) {
     if (T <= 0 || I <= 0) return MSGL_OK;
     if (act != 0 && act != 1) return MSGL_ERR_SIZE;
-    if (T > 65535) return MSGL_ERR_SIZE;
-    const dim3 grid(min((I + 255) / 256, 64), T);
-    if (dtype == MSGL_F32)
-        gated_act_kernel<float><<<grid, 256, 0, stream>>>(in, in_stride, gate_off, up_off, out, out_stride, out_off, I, act);
-    else if (dtype == MSGL_BF16)
-        gated_act_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(in, in_stride, gate_off, up_off, out, out_stride, out_off, I, act);
-    else
-        return MSGL_ERR_DTYPE;
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    const size_t item = dtype == MSGL_F32 ? 4 : 2;
+    const bool v2 = even_all(I, in_stride, gate_off, up_off, out_stride, out_off) && aligned_to(in, 2 * item) && aligned_to(out, 2 * item);
+    const int per = v2 ? 2 : 1;
+    const dim3 grid(T, max(1, min((I + 256 * per - 1) / (256 * per), 64)));
+    if (dtype == MSGL_F32) {
+        if (v2) gated_act_kernel<float, 2><<<grid, 256, 0, stream>>>(in, in_stride, gate_off, up_off, out, out_stride, out_off, I, act);
+        else gated_act_kernel<float, 1><<<grid, 256, 0, stream>>>(in, in_stride, gate_off, up_off, out, out_stride, out_off, I, act);
+    } else {
+        if (v2) gated_act_kernel<__nv_bfloat16, 2><<<grid, 256, 0, stream>>>(in, in_stride, gate_off, up_off, out, out_stride, out_off, I, act);
+        else gated_act_kernel<__nv_bfloat16, 1><<<grid, 256, 0, stream>>>(in, in_stride, gate_off, up_off, out, out_stride, out_off, I, act);
+    }
     return msgl_check_launch();
 }
 
 // ---------------------------------------------------------------------------------------
 // out[t, h, :] = x[t, h, :] * sigmoid(gate[t, h]) * c   (x dense [T, heads, d]; gate and out in packed rows)
 // ---------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, int V>
 __global__ void head_gate_kernel(const T* __restrict__ x, const void* gate_, long long gate_stride, int gate_off, void* out_,
                                  long long out_stride, int out_off, int heads, int d, float c) {
     const long long t = blockIdx.x;
     const T* g = gate_ ? reinterpret_cast<const T*>(gate_) + t * gate_stride + gate_off : nullptr;
     T* o = reinterpret_cast<T*>(out_) + t * out_stride + out_off;
     const T* xr = x + t * heads * d;
-    for (int i = threadIdx.x; i < heads * d; i += blockDim.x) {
-        const float f = g ? sigmoidf_(to_f32<T>(g[i / d])) * c : c;
-        o[i] = from_f32<T>(to_f32<T>(xr[i]) * f);
+    for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * V; i < heads * d; i += gridDim.y * blockDim.x * V) {
+        const float f = g ? sigmoidf_(to_f32<T>(g[i / d])) * c : c;       // d even: a pair lies within one head
+        float v[2];
+        ld_v<V>(xr + i, v);
+        v[0] *= f; v[1] *= f;
+        st_v<V>(o + i, v);
     }
 }
 
@@ -821,12 +906,17 @@ MSGL_API int msgl_head_gate(const void* x, const void* gate, long long gate_stri
                             int out_off, int heads, int d, float c, int T, int dtype, cudaStream_t stream) {
     if (T <= 0) return MSGL_OK;
     if (heads <= 0 || d <= 0) return MSGL_ERR_SIZE;
-    if (dtype == MSGL_F32)
-        head_gate_kernel<float><<<T, 256, 0, stream>>>((const float*)x, gate, gate_stride, gate_off, out, out_stride, out_off, heads, d, c);
-    else if (dtype == MSGL_BF16)
-        head_gate_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16*)x, gate, gate_stride, gate_off, out, out_stride,
-                                                                out_off, heads, d, c);
-    else
-        return MSGL_ERR_DTYPE;
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    const size_t item = dtype == MSGL_F32 ? 4 : 2;
+    const bool v2 = even_all(d, out_stride, out_off) && aligned_to(x, 2 * item) && aligned_to(out, 2 * item);
+    const int per = v2 ? 2 : 1;
+    const dim3 grid(T, max(1, min((heads * d + 256 * per - 1) / (256 * per), 16)));
+    if (dtype == MSGL_F32) {
+        if (v2) head_gate_kernel<float, 2><<<grid, 256, 0, stream>>>((const float*)x, gate, gate_stride, gate_off, out, out_stride, out_off, heads, d, c);
+        else head_gate_kernel<float, 1><<<grid, 256, 0, stream>>>((const float*)x, gate, gate_stride, gate_off, out, out_stride, out_off, heads, d, c);
+    } else {
+        if (v2) head_gate_kernel<__nv_bfloat16, 2><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, gate, gate_stride, gate_off, out, out_stride, out_off, heads, d, c);
+        else head_gate_kernel<__nv_bfloat16, 1><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, gate, gate_stride, gate_off, out, out_stride, out_off, heads, d, c);
+    }
     return msgl_check_launch();
 }

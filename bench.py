@@ -545,7 +545,7 @@ def vekurax_config(size, layers, vocab, window=1024, keep_first=4):
                                 "bias_max": 2 * window, "scale": s["dim"] ** -0.5, "mask": {"size": window, "keep_first": keep_first}},
                        "right": {"heads": r_heads, "dim": 64, "vdim": 128,
                                  "decay": [1.0 - 2.0 ** (-3 - 5 * h / max(r_heads - 1, 1)) for h in range(r_heads)]},
-                       "left_scale": 0.8, "right_scale": 0.5},
+                       "left_scale": 1.0, "right_scale": 0.75},
              "mlp": {"kind": "dense", "ff": s["ff"]}}
     return {"architecture": "Vekurax", "width": s["width"], "vocab": vocab, "norm": {"eps": 1e-5}, "layers": [layer] * layers}
 

@@ -113,6 +113,7 @@ struct ConvNormParams {
     void* q_out;                                     // [T, Cq]
     void* k_cache; void* v_cache; int page_size;
     int T;
+    int one_token;                                   // every request brings one token: its block brings the state up to date itself
 };
 
 template <typename T, int V, int KMAX /* most taps: 4 or MIX_MAX_TAPS */>
@@ -191,6 +192,21 @@ __global__ void __launch_bounds__(KMAX <= 4 ? 1024 : 256) conv_norm_kvwrite_kern
             st_v<V>(vc + a, y);
         }
     }
+    if (p.one_token && K > 1) {
+        // the request's only token of the step: its state moves up by one row.  A thread moves the channels it summed itself,
+        // row by row from the oldest, so every row is read before it is written; all reads of the sums lie behind the barrier.
+        T* stw = reinterpret_cast<T*>(p.state) + (size_t)slot * (K - 1) * C;
+        for (int c = threadIdx.x * V; c < C; c += blockDim.x * V) {
+            const int col = c < p.Cq ? p.q_off + c : p.k_off + (c - p.Cq);
+            float v[2];
+            for (int k = 0; k + 1 < K - 1; ++k) {
+                ld_v<V>(stw + (size_t)(k + 1) * C + c, v);
+                st_v<V>(stw + (size_t)k * C + c, v);
+            }
+            ld_v<V>(proj + (size_t)t * p.stride + col, v);
+            st_v<V>(stw + (size_t)(K - 2) * C + c, v);
+        }
+    }
 }
 
 template <typename T>
@@ -222,7 +238,7 @@ MSGL_API int msgl_conv_norm_kvwrite(const void* proj, long long stride, int q_of
                                     int taps, const float* wq_conv, const float* wk_conv, const float* wq_norm,
                                     const float* wk_norm, float eps, void* state, const int* token_req, const int* q_start,
                                     const int* slots, const int* out_loc, void* q_out, void* k_cache, void* v_cache,
-                                    int page_size, int T, int B, int dtype, cudaStream_t stream) {
+                                    int page_size, int T, int B, int one_token, int dtype, cudaStream_t stream) {
     if (T <= 0) return MSGL_OK;
     if (taps < 1 || taps > MIX_MAX_TAPS || Cq <= 0 || Ck <= 0 || d <= 0 || Ck != n_kv * d) return MSGL_ERR_SIZE;
     ConvNormParams p;
@@ -230,6 +246,7 @@ MSGL_API int msgl_conv_norm_kvwrite(const void* proj, long long stride, int q_of
     p.wq_conv = wq_conv; p.wk_conv = wk_conv; p.wq_norm = wq_norm; p.wk_norm = wk_norm; p.eps = eps; p.state = state;
     p.token_req = token_req; p.q_start = q_start; p.slots = slots; p.out_loc = out_loc; p.q_out = q_out;
     p.k_cache = k_cache; p.v_cache = v_cache; p.page_size = page_size; p.T = T;
+    p.one_token = (one_token && T == B) ? 1 : 0;
     const size_t smem = (size_t)(Cq + Ck) * sizeof(float);
     if (smem > 200 * 1024) return MSGL_ERR_SIZE;
     if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
@@ -241,7 +258,9 @@ MSGL_API int msgl_conv_norm_kvwrite(const void* proj, long long stride, int q_of
     const int per = v2 ? 2 : 1;
     const int C = Cq + Ck;
     const bool few = taps <= 4;
-    const int threads = !few ? 256 : (C / per >= 2048 ? 1024 : (C / per >= 512 ? 512 : 256));
+    // many tokens: small blocks, several a multiprocessor, so that one block's loads overlap another's sums and stores; few
+    // tokens: one large block a token
+    const int threads = (!few || T >= 256) ? 256 : (C / per >= 2048 ? 1024 : (C / per >= 512 ? 512 : 256));
 #define CONV_LAUNCH(T, V, KM)                                                                                         \
     do {                                                                                                              \
         static MsglOncePerDevice once;                                                                                \
@@ -257,7 +276,7 @@ MSGL_API int msgl_conv_norm_kvwrite(const void* proj, long long stride, int q_of
     else { if (v2) CONV_LAUNCH_K(__nv_bfloat16, 2); else CONV_LAUNCH_K(__nv_bfloat16, 1); }
 #undef CONV_LAUNCH_K
 #undef CONV_LAUNCH
-    if (taps > 1) {
+    if (taps > 1 && !p.one_token) {
         const dim3 grid(B, (C + 255) / 256);
         if (dtype == MSGL_F32)
             conv_state_update_kernel<float><<<grid, 256, 0, stream>>>(proj, stride, q_off, k_off, Cq, Ck, taps, state, q_start, slots);

@@ -661,7 +661,7 @@ def _mix_lib():
         lib.msgl_dyntanh.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
                                      c_int, c_void_p]
         lib.msgl_conv_norm_kvwrite.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_int] + [c_void_p] * 4 + \
-            [c_float] + [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_void_p]
+            [c_float] + [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.msgl_window_attention.argtypes = [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_ll, c_int,
                                               c_void_p, c_ll, c_int] + [c_int] * 9 + [c_float, c_float, c_int, c_void_p]
         lib.msgl_decay_attention.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int] + [c_void_p] * 5 + \
@@ -707,11 +707,12 @@ def dyntanh(weight: torch.Tensor, bias: torch.Tensor, alpha: float, *, x: Option
 def conv_norm_kvwrite(q_in: torch.Tensor, k_in: torch.Tensor, *, n_kv: int, head_dim: int, q_taps: torch.Tensor, k_taps: torch.Tensor,
                       q_norm: torch.Tensor, k_norm: torch.Tensor, eps: float, state: torch.Tensor, token_req: torch.Tensor,
                       q_start: torch.Tensor, slots: torch.Tensor, out_loc: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
-                      v_cache: Optional[torch.Tensor], page_size: int) -> torch.Tensor:
+                      v_cache: Optional[torch.Tensor], page_size: int, one_token: bool = False) -> torch.Tensor:
     """Short causal convolution over time on every channel of q_in [T, Cq] and k_in [T, Ck] (views into one packed
     projection), continued from `state` [slots, taps - 1, Cq + Ck] (the request's last inputs, which the call brings up to
     date), then an RMS norm over the whole of q and of k.  The normed k goes to `k_cache`, the un-normed k to `v_cache`
-    (layout [page][kv head][slot][head_dim]) at token slots `out_loc`; the normed q comes back as [T, Cq]."""
+    (layout [page][kv head][slot][head_dim]) at token slots `out_loc`; the normed q comes back as [T, Cq].  one_token: every
+    request brings exactly one token (the state is then brought up to date by the same launch)."""
     _need_cuda(q_in, k_in, q_taps, k_taps, q_norm, k_norm, state, token_req, q_start, slots, out_loc, k_cache, v_cache)
     T, Cq, Ck = q_in.shape[0], q_in.shape[1], k_in.shape[1]
     stride = _rows_view(q_in, Cq, "q")
@@ -731,10 +732,10 @@ def conv_norm_kvwrite(q_in: torch.Tensor, k_in: torch.Tensor, *, n_kv: int, head
     code = _mix_lib().msgl_conv_norm_kvwrite(_ptr(q_in), stride, q_off, k_off, Cq, Ck, head_dim, n_kv, taps, _ptr(q_taps), _ptr(k_taps),
                                              _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(state), _ptr(token_req), _ptr(q_start),
                                              _ptr(slots), _ptr(out_loc), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), page_size, T, B,
-                                             _dt(q_in), _stream())
+                                             int(bool(one_token)), _dt(q_in), _stream())
     _check(code, f"conv_norm_kvwrite ({taps} taps)")
     global LAUNCHES
-    LAUNCHES += int(taps > 1)
+    LAUNCHES += int(taps > 1 and not (one_token and T == B))
     return q_out
 
 

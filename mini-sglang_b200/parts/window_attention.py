@@ -57,7 +57,7 @@ class ConvWindowAttention(Mixer, Projected):
         self.window = int(s["window"]) if s.get("window") else None
         self.keep_first = int(s.get("keep_first", 0)) if self.window else 0
         self.bias_far = float(s["bias_far"])
-        self.bias_rows = int(s.get("bias_rows", 32))
+        self.bias_rows = int(s.get("bias_rows", 48))
         self.Cq, self.Ck = self.n_q * self.d, self.n_kv * self.d
         names = {"q": "q", "k": "k", "q_norm": "q_norm", "k_norm": "k_norm", "q_conv": "q_conv", "k_conv": "k_conv",
                  "bias": "distance_bias", "gate": "gate", "out": "out"}
@@ -114,7 +114,7 @@ class ConvWindowAttention(Mixer, Projected):
                                   k_taps=self.k_taps, q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps, state=conv.state,
                                   token_req=ctx.token_req, q_start=ctx.q_start, slots=ctx.slots,
                                   out_loc=kv.group.out_loc if writes_cache else None, k_cache=kv.k if writes_cache else None,
-                                  v_cache=kv.v if writes_cache else None, page_size=kv.page_size)
+                                  v_cache=kv.v if writes_cache else None, page_size=kv.page_size, one_token=ctx.uniform_decode)
         gate = proj[:, Cq + Ck:Cq + Ck + self.n_q]
         if self.use_mma:
             q3 = q.view(ctx.T, self.n_q, self.d)

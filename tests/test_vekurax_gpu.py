@@ -115,7 +115,7 @@ def test_gated_activation_and_rms_gate(act):
 
 def test_distance_buckets_equal_the_plain_ones():
     from mini_sglang_b200.parts.window_attention import distance_buckets
-    for rows, far in ((32, 240), (10, 37), (2, 5), (15, 200), (16, 256), (1, 9), (64, 1000)):
+    for rows, far in ((24, 300), (10, 37), (2, 5), (15, 200), (16, 256), (1, 9), (64, 1000)):
         n = int(far) + 40
         got = distance_buckets(rows, far, n).tolist()
         want = [pv.distance_bucket(k, rows, far) if rows > 1 else 0 for k in range(n)]
@@ -124,7 +124,8 @@ def test_distance_buckets_equal_the_plain_ones():
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("taps,cuts", [(4, (1, 2, 1, 5, 3, 11)), (2, (7, 1, 1, 14)), (1, (23,)), (5, (2, 2, 2, 2, 15))])
+@pytest.mark.parametrize("taps,cuts", [(4, (1, 2, 1, 5, 3, 11)), (2, (7, 1, 1, 14)), (1, (23,)), (5, (2, 2, 2, 2, 15)),
+                                       (4, (3, 1, 1, 1, 1, 1, 1, 3)), (3, (1,) * 9), (6, (1,) * 8)])
 def test_convolution_norm_and_cache_write_in_portions(dtype, taps, cuts):
     """Two requests fed in different portions in the same steps: the convolution continues from each request's own state,
     and the cache receives the normed keys and the un-normed keys as values at the given slots."""
@@ -158,7 +159,7 @@ def test_convolution_norm_and_cache_write_in_portions(dtype, taps, cuts):
         out_loc = torch.tensor(sum((loc[r][at[r]:at[r] + n] for r, n in zip(reqs, ns)), []), dtype=torch.int32).cuda()
         q = ops.conv_norm_kvwrite(x[:, :Cq], x[:, Cq:Cq + Ck], n_kv=G, head_dim=d, q_taps=qt.cuda(), k_taps=kt.cuda(), q_norm=qn.cuda(),
                                   k_norm=kn.cuda(), eps=eps, state=state, token_req=token_req, q_start=q_start, slots=slots,
-                                  out_loc=out_loc, k_cache=kc, v_cache=vc, page_size=P)
+                                  out_loc=out_loc, k_cache=kc, v_cache=vc, page_size=P, one_token=all(n == 1 for n in ns))
         o = 0
         for r, n in zip(reqs, ns):
             got_q[r].append(q[o:o + n].float().cpu())
@@ -280,15 +281,15 @@ def test_window_attention_other_geometries(dtype):
     # one head per kv head, a window of one token, a table of two rows, pages of one token
     _window_case(dtype, H=3, G=3, d=16, P=1, window=1, keep_first=4, rows=2, far=5, ctx=40, n_new=5, spike_at=("abs", 3), seed=2)
     # no kept tokens, head size above 128, nothing cached before the portion (the first tokens of a sequence)
-    _window_case(dtype, H=2, G=2, d=160, P=8, window=33, keep_first=0, rows=32, far=240, ctx=0, n_new=70, spike_at=(32,), seed=3)
+    _window_case(dtype, H=2, G=2, d=160, P=8, window=33, keep_first=0, rows=20, far=130, ctx=0, n_new=70, spike_at=(32,), seed=3)
     _window_case(dtype, H=2, G=1, d=40, P=4, window=5, keep_first=17, rows=8, far=64, ctx=0, n_new=2, spike_at=(1,), seed=4)
     # decoding the second token of a sequence; decoding with the window's far edge on a page border
     _window_case(dtype, H=4, G=2, d=32, P=4, window=8, keep_first=2, rows=8, far=64, ctx=1, n_new=1, spike_at=(1,), seed=5)
     _window_case(dtype, H=4, G=2, d=32, P=4, window=8, keep_first=2, rows=8, far=64, ctx=31, n_new=1, spike_at=(7,), seed=6)
     # a window of several key tiles with kept tokens far before it: a decoded token, a short run and a long portion
     for n_new in (1, 3, 90):
-        _window_case(dtype, H=8, G=2, d=96, P=16, window=200, keep_first=70, rows=32, far=240, ctx=700, n_new=n_new, spike_at=("abs", 69), seed=7)
-        _window_case(dtype, H=8, G=2, d=96, P=16, window=200, keep_first=70, rows=32, far=240, ctx=700, n_new=n_new, spike_at=(199,), seed=8)
+        _window_case(dtype, H=8, G=2, d=96, P=16, window=200, keep_first=70, rows=24, far=300, ctx=700, n_new=n_new, spike_at=("abs", 69), seed=7)
+        _window_case(dtype, H=8, G=2, d=96, P=16, window=200, keep_first=70, rows=24, far=300, ctx=700, n_new=n_new, spike_at=(199,), seed=8)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -19,7 +19,7 @@ import torch
 
 
 def _layer(width, *, heads, kv_heads, dim, window, keep_first, taps, far, scale=None, r_heads, r_dim, r_vdim, decay, ff,
-           left_scale=0.8, right_scale=0.5, weights_of=None):
+           left_scale=0.9, right_scale=0.6, weights_of=None):
     entry = {"type": "parallel",
              "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "conv": taps, "bias_max": far,
                                 "scale": scale if scale is not None else dim ** -0.5,

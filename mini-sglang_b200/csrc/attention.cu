@@ -1574,8 +1574,12 @@ static int attention_launch(const void* q, void* out, const void* k_cache, const
 MSGL_API int msgl_attention_tc(const void* q, void* out, const void* k_cache, const void* v_cache, const int* q_start,
                                const int* kv_len, const int* block_table, int B, int T_, int n_q, int n_kv, int d,
                                int page_size, int bt_stride, int window, float scale, int qlen_min, int qlen_max,
-                               int grid_x, int cache_pages, int version, int* status, cudaStream_t stream) {
+                               int grid_x, int cache_pages, int version, int* status, int keep_first, const float* bias,
+                               int bias_len, cudaStream_t stream) {
 #if MSGL_HEAD_DIM == 128
+    // kept first tokens under the window and a bias by distance ([n_q][bias_len] float32, log2 units): version 2 only
+    const bool ext = (window > 0 && keep_first > 0) || bias != nullptr;
+    if (ext && (version != 2 || keep_first < 0 || (bias != nullptr && bias_len < 1))) return MSGL_ERR_SIZE;
     if (grid_x <= 0 || B <= 0) return MSGL_OK;
     if (d != 128 || n_kv <= 0 || n_q % n_kv != 0 || page_size <= 0 || grid_x > 65535) return MSGL_ERR_SIZE;
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return MSGL_ERR_ALIGN;
@@ -1588,13 +1592,15 @@ MSGL_API int msgl_attention_tc(const void* q, void* out, const void* k_cache, co
     p.page_shift = -1;
     if ((page_size & (page_size - 1)) == 0) { int sh = 0; while ((1 << sh) < page_size) ++sh; p.page_shift = sh; }
     p.scale = scale; p.qlen_min = qlen_min; p.qlen_max = qlen_max; p.uniform_decode = 0;
+    p.keep_first = window > 0 ? keep_first : 0; p.bias = bias; p.bias_len = bias_len;
     const int G = n_q / n_kv;
     const int n_chunks = G <= TC_ROWS ? 1 : (G + TC_ROWS - 1) / TC_ROWS;
     const size_t smem = (size_t)TC_SMEM_BYTES + 1024;
     static MsglOncePerDevice attr_set;
     if (attr_set.due()) {      // first call on this device, never inside a stream capture
         if (cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-            cudaFuncSetAttribute(attn_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC2_SMEM_ALLOC) != cudaSuccess)
+            cudaFuncSetAttribute(attn_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC2_SMEM_ALLOC) != cudaSuccess ||
+            cudaFuncSetAttribute(attn_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC2_SMEM_ALLOC) != cudaSuccess)
             return msgl_check_launch();
         attr_set.mark();
     }
@@ -1610,7 +1616,8 @@ MSGL_API int msgl_attention_tc(const void* q, void* out, const void* k_cache, co
     }
     if (version == 2) {
         if (tma_box == 0) return MSGL_ERR_SIZE;
-        attn_tc2_kernel<<<dim3(n_kv * n_chunks, grid_x, 1), TC2_THREADS, TC2_SMEM_ALLOC, stream>>>(p, status, kmap, vmap, tma_box);
+        if (ext) attn_tc2_kernel<true><<<dim3(n_kv * n_chunks, grid_x, 1), TC2_THREADS, TC2_SMEM_ALLOC, stream>>>(p, status, kmap, vmap, tma_box);
+        else attn_tc2_kernel<false><<<dim3(n_kv * n_chunks, grid_x, 1), TC2_THREADS, TC2_SMEM_ALLOC, stream>>>(p, status, kmap, vmap, tma_box);
         return msgl_check_launch();
     }
     attn_tc_kernel<<<dim3(n_kv * n_chunks, grid_x, 1), TC_THREADS, smem, stream>>>(p, status, kmap, vmap, tma_box);

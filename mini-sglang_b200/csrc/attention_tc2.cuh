@@ -47,6 +47,10 @@ constexpr int TC2_THREADS = 384;
 constexpr unsigned TC2_SMEM_BYTES = 2u * TC_Q_BYTES + 4u * TC_KV_BYTES;      // 192 KB
 constexpr unsigned TC2_SMEM_ALLOC = TC2_SMEM_BYTES + 256u + 1024u;
 
+// EXT: the launch has kept first tokens under its window or a bias by distance (AttnParams::keep_first, bias): the key tiles
+// that hold kept tokens before the window's first tile are walked ahead of the window's, and every score gets its table entry.
+// Without EXT none of that is compiled in.
+template <bool EXT>
 __global__ void __launch_bounds__(TC2_THREADS, 1) attn_tc2_kernel(const AttnParams p, int* status,
                                                                   const __grid_constant__ CUtensorMap kmap,
                                                                   const __grid_constant__ CUtensorMap vmap, int tma_box) {
@@ -91,8 +95,12 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) attn_tc2_kernel(const AttnPara
     const int pmax_a = p_min + ntok_a - 1;
     const int k_lo = p.window > 0 ? max(0, p_min - p.window + 1) : 0;
     const int kt_begin = k_lo / TC_KT;
-    const int n_a = pmax_a / TC_KT + 1 - kt_begin;                        // key tiles of tile A
-    const int n_b = ntok_b > 0 ? p_max / TC_KT + 1 - kt_begin : 0;         // key tiles of tile B (0: no token there)
+    // kept first tokens before the window's first tile: keys [0, sink_hi) in n_sink tiles that come first for both query tiles
+    const int sink_hi = (EXT && p.window > 0) ? min(p.keep_first, kt_begin * TC_KT) : 0;
+    const int n_sink = (sink_hi + TC_KT - 1) / TC_KT;
+    auto tile_of = [&](int j) -> int { return (EXT && j < n_sink) ? j : kt_begin + (j - n_sink); };
+    const int n_a = pmax_a / TC_KT + 1 - kt_begin + n_sink;               // key tiles of tile A
+    const int n_b = ntok_b > 0 ? p_max / TC_KT + 1 - kt_begin + n_sink : 0;  // key tiles of tile B (0: no token there)
     const int n_tiles = max(n_a, n_b);
 
     if (tid == 0) {
@@ -134,18 +142,20 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) attn_tc2_kernel(const AttnPara
         const int n_box = TC_KT / tma_box;
         unsigned vt_phase = 0;
         auto box_row = [&](int j) -> int {            // first cache row of this lane's box of tile j, or -1
-            const int key_b = (kt_begin + j) * TC_KT + lane * tma_box;
+            const int key_b = tile_of(j) * TC_KT + lane * tma_box;
             if (j >= n_tiles || lane >= n_box || key_b > p_max) return -1;          // boxes past the last visible key are not fetched
+            if (EXT && j < n_sink && key_b >= sink_hi) return -1;                   // nor those past the last kept token
             return (bt[page_index(p, key_b)] * p.n_kv + kvh) * p.page_size + page_slot(p, key_b);
         };
         int y = box_row(0);
         for (int j = 0; j < n_tiles; ++j) {
             const int st = j & 1;
             const int y_next = box_row(j + 1);                                    // looked up a tile ahead
-            const int key0 = (kt_begin + j) * TC_KT;
+            const int key0 = tile_of(j) * TC_KT;
+            const int last_key = (EXT && j < n_sink) ? sink_hi - 1 : p_max;      // the tile's rows behind it hold nothing that may be read
             const unsigned dst_tile = (is_k ? k_s : v_s) + (unsigned)st * TC_KV_BYTES;
             const unsigned n_act = __popc(__ballot_sync(0xffffffffu, y >= 0));
-            const bool ragged = !is_k && p_max < key0 + TC_KT - 1;               // V rows past p_max have to be zero
+            const bool ragged = !is_k && last_key < key0 + TC_KT - 1;            // V rows past the last key have to be zero
             if (j >= 2 && !tc_mbar_wait(is_k ? bar_kr(st) : bar_vr(st), ((j >> 1) - 1) & 1)) { fail = 1; break; }   // tile j-2 has been read
             const unsigned bar = ragged ? bar_vt : (is_k ? bar_kf(st) : bar_vf(st));
             if (lane == 0) tc_mbar_expect_tx(bar, n_act * 2u * (unsigned)tma_box * 128u);
@@ -157,7 +167,7 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) attn_tc2_kernel(const AttnPara
             if (ragged) {
                 if (!tc_mbar_wait(bar_vt, vt_phase)) { fail = 1; break; }
                 vt_phase ^= 1u;
-                const int r0 = p_max + 1 - key0;                                 // first row without a visible key
+                const int r0 = last_key + 1 - key0;                              // first row without a visible key
                 for (int idx = r0 * 16 + lane; idx < TC_KT * 16; idx += 32) {
                     const unsigned a = dst_tile + (unsigned)((idx >> 3) & 1) * TC_KHALF_BYTES + (unsigned)(idx >> 4) * 128u + (unsigned)(idx & 7) * 16u;
                     asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(a), "r"(0u) : "memory");
@@ -242,6 +252,9 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) attn_tc2_kernel(const AttnPara
         const bool my_valid = row / Gc < QH && my_tl < ti.n_tok && (chunk * TC_ROWS + row % Gc) < G;
         const int pmin_x = p_min + x * QH, pmax_x = x ? p_max : pmax_a;
         const float sc = p.scale * 1.4426950408889634f;
+        const float inv_sc = 1.f / sc;
+        const float* my_bias = (EXT && p.bias != nullptr)
+            ? p.bias + (size_t)min(kvh * G + chunk * TC_ROWS + row % Gc, p.n_q - 1) * p.bias_len : nullptr;
         float m_run = -INFINITY, l_run = 0.f, o_scale = 1.f;
 #ifdef MSGL_TC_PROFILE
         long long tp[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -254,19 +267,39 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) attn_tc2_kernel(const AttnPara
             if (!tc_mbar_wait(bar_s(x), it & 1)) { fail = 1; break; }
             tc_fence_after();
             TC2_MARK(0)
-            const int key0 = (kt_begin + it) * TC_KT;
-            const bool need_mask = (key0 + TC_KT - 1 > pmin_x) || (p.window > 0 && key0 <= pmax_x - p.window);
+            const int key0 = tile_of(it) * TC_KT;
+            const bool in_sink = EXT && it < n_sink;
+            const bool need_mask = in_sink || (key0 + TC_KT - 1 > pmin_x) || (p.window > 0 && key0 <= pmax_x - p.window);
             float s0[32], s1[32], s2[32], s3[32];
             tc_ld32(ts, s0); tc_ld32(ts + 32, s1); tc_ld32(ts + 64, s2); tc_ld32(ts + 96, s3);
             tc_wait_ld(s0); tc_wait_ld(s1); tc_wait_ld(s2); tc_wait_ld(s3);
             TC2_MARK(1)
+            if (EXT && p.bias != nullptr) {
+                // the row's table entries for this tile lie side by side, by falling distance; they are in log2 units and
+                // the scores still unscaled, so they go in divided by the scale that the exponent applies
+                const int d0 = my_pos - key0;                                     // distance to the tile's first key
+                const bool inside = d0 - (TC_KT - 1) >= 0 && d0 <= p.bias_len - 1;
+                auto add_bias = [&](float (&sv)[32], int cb) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int dist = d0 - (cb * 32 + j);
+                        sv[j] = fmaf(my_bias[inside ? dist : min(max(dist, 0), p.bias_len - 1)], inv_sc, sv[j]);
+                    }
+                };
+                add_bias(s0, 0); add_bias(s1, 1); add_bias(s2, 2); add_bias(s3, 3);
+            }
             if (need_mask) {
                 auto mask = [&](float (&sv)[32], int cb) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int key = key0 + cb * 32 + j;
                         bool okk = key <= my_pos;
-                        if (p.window > 0) okk = okk && (key > my_pos - p.window);
+                        if (EXT) {
+                            if (p.window > 0) okk = okk && (key > my_pos - p.window || key < p.keep_first);
+                            if (in_sink) okk = okk && key < sink_hi;
+                        } else if (p.window > 0) {
+                            okk = okk && (key > my_pos - p.window);
+                        }
                         if (!okk) sv[j] = -INFINITY;
                     }
                 };

@@ -111,7 +111,7 @@ def _attn_lib(head_dim: int):
         lib.msgl_attention.argtypes = [c_void_p] * 10 + [c_int] * 9 + [c_float] + [c_int] * 6 + [c_void_p, c_void_p, c_int, c_void_p]
         lib.msgl_attention_window.argtypes = [c_void_p] * 10 + [c_int] * 9 + [c_float] + [c_int] * 6 + [c_void_p, c_int, c_void_p, c_int, c_void_p]
         lib.msgl_attention_combine.argtypes = [c_void_p] * 5 + [c_int] * 5 + [c_void_p]
-        lib.msgl_attention_tc.argtypes = [c_void_p] * 7 + [c_int] * 8 + [c_float] + [c_int] * 5 + [c_void_p, c_void_p]
+        lib.msgl_attention_tc.argtypes = [c_void_p] * 7 + [c_int] * 8 + [c_float] + [c_int] * 5 + [c_void_p, c_int, c_void_p, c_int, c_void_p]
         lib.msgl_attention_head_dim.restype = c_int
         _attn[hd] = lib
     return lib
@@ -367,9 +367,12 @@ _tc2_usable = True
 
 def attention_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *,
                  q_start: torch.Tensor, kv_len: torch.Tensor, block_table: torch.Tensor, n_kv: int, page_size: int,
-                 window: int, scale: float, qlen_min: int, qlen_max: int, q_lens: Sequence[int]) -> None:
+                 window: int, scale: float, qlen_min: int, qlen_max: int, q_lens: Sequence[int], keep_first: int = 0,
+                 bias_log2: Optional[torch.Tensor] = None) -> bool:
     """Prefill attention on tcgen05 tensor cores for the requests with q_len in [qlen_min, qlen_max];
-    q_lens: the host's copy of every request's number of query tokens (to size the grid)."""
+    q_lens: the host's copy of every request's number of query tokens (to size the grid).  keep_first, bias_log2: as in
+    `attention`; they are taken by the kernel on pairs of query tiles only (TMA page sizes), and the call returns False,
+    having launched nothing, where that kernel cannot run."""
     global _tc2_usable
     _need_cuda(q, out, k_cache, v_cache, q_start, kv_len, block_table)
     T, n_q, d = q.shape
@@ -381,6 +384,14 @@ def attention_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_ca
     pages = k_cache.shape[0] if whole else 0
     tma_pages = whole and page_size >= 8 and (page_size & (page_size - 1)) == 0
     versions = [2, 1] if (TC_VERSION == 2 and _tc2_usable and tma_pages) else [1]
+    ext = bool(keep_first) or bias_log2 is not None
+    if ext:
+        _need_cuda(bias_log2)
+        if versions[0] != 2:
+            return False
+        versions = [2]
+        if bias_log2 is not None:
+            assert bias_log2.dtype == torch.float32 and bias_log2.dim() == 2 and bias_log2.shape[0] == n_q and bias_log2.is_contiguous()
     for version in versions:
         rows = TC_ROWS * version
         qt = rows // group if group <= TC_ROWS else version
@@ -388,12 +399,15 @@ def attention_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_ca
         code = _attn_lib(d).msgl_attention_tc(
             _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table), B, T, n_q,
             n_kv, d, page_size, block_table.stride(0), window, float(scale), qlen_min, qlen_max, grid_x, pages, version,
-            _ptr(status), _stream())
+            _ptr(status), int(keep_first), _ptr(bias_log2), bias_log2.shape[1] if bias_log2 is not None else 0, _stream())
         if code == 2 and version == 2:        # no tensor maps here (driver without the encoder, unaligned cache): one-tile kernel
             _tc2_usable = False
+            if ext:
+                return False
             continue
         _check(code, "attention_tc")
-        return
+        return True
+    return False
 
 
 def attention_tile_tokens(variant: int, group: int, head_dim: int = 128) -> int:

@@ -109,7 +109,7 @@ def paged_attend(q: torch.Tensor, out: torch.Tensor, ctx: StepContext, cache: KV
     """The attention launches of one step over a paged cache: requests that bring a few tokens through the decode kernel
     with the step's kv splits, longer runs through the prefill kernels, the merge of the splits.  keep_first and bias_log2
     (kept first tokens under a window, a bias by distance: `ops.attention`) are for mixers that have them; such launches
-    stay on the mma kernels."""
+    run on the tcgen05 prefill kernel on pairs of query tiles where it applies and on the mma kernels otherwise."""
     plain = keep_first == 0 and bias_log2 is None
     if not plain and not use_mma:
         raise ValueError("kept first tokens and a distance bias are taken by the bfloat16 mma kernels only")
@@ -147,11 +147,12 @@ def paged_attend(q: torch.Tensor, out: torch.Tensor, ctx: StepContext, cache: KV
             # the tcgen05 kernels take whole key ranges: only if no longer request has kv splits
             unsplit = max_split == 1 or (g.host_nsplit is not None and
                                          all(ns == 1 for n, ns in zip(ctx.host_q_lens, g.host_nsplit) if n > qt_dec))
-            if n_row and plain and unsplit and ops.tc_supported(d, q.dtype, G):
-                ops.attention_tc(q, out, cache.k, cache.v, q_start=ctx.q_start, kv_len=ctx.kv_len,
-                                 block_table=g.block_table, n_kv=n_kv, page_size=cache.page_size, window=window,
-                                 scale=scale, qlen_min=qt_dec + 1, qlen_max=big, q_lens=ctx.host_q_lens)
-            elif n_row:
+            on_tc = False
+            if n_row and unsplit and ops.tc_supported(d, q.dtype, G):
+                on_tc = ops.attention_tc(q, out, cache.k, cache.v, q_start=ctx.q_start, kv_len=ctx.kv_len,
+                                         block_table=g.block_table, n_kv=n_kv, page_size=cache.page_size, window=window,
+                                         scale=scale, qlen_min=qt_dec + 1, qlen_max=big, q_lens=ctx.host_q_lens, **extra)
+            if n_row and not on_tc:
                 ops.attention(q, out, cache.k, cache.v, qlen_min=qt_dec + 1, qlen_max=big,
                               variant=ops.VARIANT_MMA_ROWS, grid_x=n_row, **common)
     if max_split > 1:

@@ -147,3 +147,21 @@ def test_plain_sequence_is_causal_and_runs_shared_weights():
     streams = []
     pv.forward_sequence(cfg, w, toks, streams=streams)
     assert len(streams) == len(cfg["layers"])
+
+
+def test_a_window_or_kept_token_one_off_would_show():
+    """The bound of the model-level comparisons on the GPU (an rms error of 2.5 % of a row's rms in bfloat16) can fail: the plain
+    implementation with the window one token wider or narrower, or one kept token more or fewer, moves every row behind the
+    window by at least twice that."""
+    cfg = config_json(CONFIGS_V["VA"])
+    w = make_weights(CONFIGS_V["VA"], 3)
+    toks = random_tokens(60, cfg["vocab"], 9)
+    base = pv.forward_sequence(cfg, w, toks).float()
+    for key, delta in (("size", 1), ("size", -1), ("keep_first", -1), ("keep_first", 1)):
+        other = json.loads(json.dumps(cfg))
+        for layer in other["layers"]:
+            if layer["mixer"]["left"]["mask"][key] + delta >= 0:
+                layer["mixer"]["left"]["mask"][key] += delta
+        moved = pv.forward_sequence(other, w, toks).float()
+        err = (moved - base).pow(2).mean(1).sqrt() / base.pow(2).mean(1).sqrt()
+        assert float(err[20:].min()) > 0.045, (key, delta, float(err[20:].min()))

@@ -19,7 +19,7 @@ import pytest
 import torch
 
 import plain_vekurax as pv
-from helpers import assert_row_close, assert_rows_close, play
+from helpers import assert_row_close, play
 from tiny_models import random_tokens, write_model_dir
 from tiny_vekurax import CONFIGS_V, config_json, make_weights
 
@@ -53,12 +53,31 @@ def runner(name, dtype, num_pages, max_reqs=4, page_size=None, graphs=True):
                                       max_reqs=max_reqs, max_context_len=4096, use_cuda_graph=graphs)
 
 
+# bfloat16: a layer of this design rounds to 8 mantissa bits at more places than a plain attention layer (what leaves the
+# convolution, the normed q and k, both mixers' gated outputs, the activation), and a run of the layer list twice doubles them:
+# the rounding noise of the logits is up to about 1.7 % of a row's rms at these small widths.  The bound is 2.5 %; a window one
+# token off or one kept token fewer moves every row behind the window by 5 % or more (tests/test_vekurax_cpu.py).
+BF16_RMS_FRACTION_V = 0.025
+
+
+def row_close(row, want, dtype):
+    if dtype == "float32":
+        return assert_row_close(row, want, dtype)
+    row, want = row.float(), want.float()
+    assert torch.isfinite(row).all(), "logits are not finite"
+    err = row - want
+    scale = want.pow(2).mean().sqrt().item()
+    rms, worst = err.pow(2).mean().sqrt().item(), err.abs().max().item()
+    assert rms <= BF16_RMS_FRACTION_V * scale, f"rms error {rms:.4g} is {rms / scale:.2%} of the row's rms {scale:.4g}"
+    assert worst <= 6.0 * BF16_RMS_FRACTION_V * scale, f"largest error {worst:.4g} is {worst / scale:.2%} of the row's rms {scale:.4g}"
+
+
 def compare(name, dtype, got, seqs):
     assert got
     for (rid, pos), row in sorted(got.items()):
         want = plain(name, tuple(seqs[rid]))[pos]
         try:
-            assert_row_close(row, want, dtype)
+            row_close(row, want, dtype)
         except AssertionError as e:
             raise AssertionError(f"request {rid!r} position {pos} ({dtype}, {name}): {e}") from None
 
@@ -197,17 +216,18 @@ def _window_case(dtype, *, H, G, d, P, window, keep_first, rows, far, ctx, n_new
     rel = torch.randn(rows, H, generator=g)
     gate = torch.randn(n_new, H, generator=g).to(dt).float()
     scale = 0.5
-    # plain
+    # plain: every query by itself over the keys it may see
     want = torch.zeros(n_new, H, d, dtype=torch.float64)
-    for h in range(H):
-        kvh = h // (H // G)
-        for t in range(n_new):
-            i = ctx + t
-            js = [j for j in range(i + 1) if pv.visible(i, j, window, keep_first)]
-            s = torch.tensor([float((q[t, h].double() * k[j, kvh].double()).sum()) * scale +
-                              float(rel[pv.distance_bucket(i - j, rows, far) if rows > 1 else 0, h]) for j in js], dtype=torch.float64)
-            a = torch.softmax(s, 0)
-            want[t, h] = (a[:, None] * v[js, kvh].double()).sum(0) * torch.sigmoid(gate[t, h].double()) * 1.25
+    bucket = torch.tensor([pv.distance_bucket(n, rows, far) if rows > 1 else 0 for n in range(L)])
+    qd_, kd_, vd_ = q.double(), k.double(), v.double()
+    for t in range(n_new):
+        i = ctx + t
+        js = torch.tensor([j for j in range(i + 1) if pv.visible(i, j, window, keep_first)])
+        for h in range(H):
+            kvh = h // (H // G)
+            sc_ = (kd_[js, kvh] @ qd_[t, h]) * scale + rel[bucket[i - js], h].double()
+            a = torch.softmax(sc_, 0)
+            want[t, h] = (a[:, None] * vd_[js, kvh]).sum(0) * torch.sigmoid(gate[t, h].double()) * 1.25
     # engine kernel over a paged cache with shuffled pages
     n_pages = -(-L // P)
     perm = torch.randperm(n_pages + 3, generator=g)[:n_pages] + 1
@@ -253,6 +273,18 @@ def _window_case(dtype, *, H, G, d, P, window, keep_first, rows, far, ctx, n_new
                 ops.attention_combine(part_o, part_ml, None if n_new == 1 else torch.zeros(n_new, dtype=torch.int32).cuda(), nsplit, o, ns)
             assert torch.isfinite(o).all(), (variant, ns)
             torch.testing.assert_close(o.float().cpu(), ungated, rtol=3e-2, atol=3e-2, msg=lambda m: f"variant {variant}, {ns} pieces: {m}")
+        if ops.tc_supported(d, dt, H // G) and n_new > ops.attention_tile_tokens(ops.VARIANT_MMA_DECODE, H // G, d):
+            # and through the tcgen05 prefill kernel (head size 128)
+            o = torch.full((n_new, H, d), float("nan"), dtype=dt).cuda()
+            done = ops.attention_tc(qd, o, kd, vd, q_start=common["q_start"], kv_len=common["kv_len"], block_table=common["block_table"],
+                                    n_kv=G, page_size=P, window=window, scale=scale, qlen_min=1, qlen_max=1 << 30, q_lens=[n_new],
+                                    keep_first=keep_first, bias_log2=bias_log2)
+            ops.check_kernel_status()
+            if done:
+                assert torch.isfinite(o).all()
+                torch.testing.assert_close(o.float().cpu(), ungated, rtol=3e-2, atol=3e-2, msg=lambda m: f"tcgen05 kernel: {m}")
+            else:
+                assert P < 8 or P & (P - 1), "the tcgen05 kernel refused a page size that TMA fetches"
     return want
 
 
@@ -286,6 +318,13 @@ def test_window_attention_other_geometries(dtype):
     # decoding the second token of a sequence; decoding with the window's far edge on a page border
     _window_case(dtype, H=4, G=2, d=32, P=4, window=8, keep_first=2, rows=8, far=64, ctx=1, n_new=1, spike_at=(1,), seed=5)
     _window_case(dtype, H=4, G=2, d=32, P=4, window=8, keep_first=2, rows=8, far=64, ctx=31, n_new=1, spike_at=(7,), seed=6)
+    # head size 128 (the tcgen05 prefill kernel): kept tokens in a tile of their own, the window's edge, the first tokens of a
+    # sequence (no tile before the window), a window wider than the context, one kv head for eight query heads
+    for spike in (("abs", 69), (199,), ("abs", 70), (200,)):
+        _window_case(dtype, H=8, G=2, d=128, P=16, window=200, keep_first=70, rows=24, far=300, ctx=700, n_new=200, spike_at=spike, seed=9)
+    _window_case(dtype, H=4, G=2, d=128, P=16, window=150, keep_first=5, rows=24, far=100, ctx=0, n_new=400, spike_at=(149,), seed=10)
+    _window_case(dtype, H=8, G=1, d=128, P=32, window=1000, keep_first=9, rows=16, far=300, ctx=100, n_new=150, spike_at=(120,), seed=11)
+    _window_case(dtype, H=2, G=2, d=128, P=8, window=130, keep_first=140, rows=6, far=50, ctx=300, n_new=260, spike_at=("abs", 139), seed=12)
     # a window of several key tiles with kept tokens far before it: a decoded token, a short run and a long portion
     for n_new in (1, 3, 90):
         _window_case(dtype, H=8, G=2, d=96, P=16, window=200, keep_first=70, rows=24, far=300, ctx=700, n_new=n_new, spike_at=("abs", 69), seed=7)
@@ -421,25 +460,6 @@ def test_long_decoding_past_every_window(dtype):
     r.mgr.check_idle()
 
 
-def test_a_window_or_kept_token_one_off_would_show():
-    """The model-level comparisons can fail: on the CPU, the plain implementation with the window one token wider or
-    one kept token fewer moves the logits behind the window by far more than the tests' bounds."""
-    name = "VA"
-    cfg = config_json(CONFIGS_V[name])
-    toks = random_tokens(40, cfg["vocab"], 9)
-    base = plain(name, tuple(toks))
-    for key, delta in (("size", 1), ("keep_first", -1)):
-        other = json.loads(json.dumps(cfg))
-        for layer in other["layers"]:
-            if layer["mixer"]["left"]["mask"][key] + delta >= 0:
-                layer["mixer"]["left"]["mask"][key] += delta
-        moved = pv.forward_sequence(other, weights(name), toks).float()
-        err = (moved[-1] - base[-1]).pow(2).mean().sqrt() / base[-1].pow(2).mean().sqrt()
-        assert err > 0.03, (key, float(err))
-        with pytest.raises(AssertionError):
-            assert_row_close(moved[-1], base[-1], "bfloat16")
-
-
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_entry_point(dtype):
     """Engine.generate with the scheduler: prompts of unequal lengths, portions of at most 16 tokens, a small pool."""
@@ -483,7 +503,7 @@ def test_trace_replay_program(tmp_path):
         assert [l for l in proc.stdout.split("\n") if l.startswith("done")] == [f"done {i}" for i in range(4)]
         ra, rb = plain(name, tuple(a)), plain(name, tuple(b))
         rd = lambda i: torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V))        # noqa: E731
-        assert_rows_close(rd(0), ra[[0, 19]], dtype)
-        assert_rows_close(rd(1), rb[[20]], dtype)
-        assert_rows_close(rd(2), ra[[35]], dtype)
-        assert_rows_close(rd(3), ra[[36]], dtype)
+        for got, want in ((rd(0), ra[[0, 19]]), (rd(1), rb[[20]]), (rd(2), ra[[35]]), (rd(3), ra[[36]])):
+            assert got.shape == want.shape
+            for g_row, w_row in zip(got, want):
+                row_close(g_row, w_row, dtype)

@@ -43,6 +43,60 @@ template <int V> __device__ __forceinline__ void st_v(float* p, const float (&o)
 template <int V> __device__ __forceinline__ void st_v(__nv_bfloat16* p, const float (&o)[2]) {
     if (V == 2) *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(o[0], o[1]); else p[0] = __float2bfloat16_rn(o[0]);
 }
+// V neighbouring elements at once, V = 1, 2 or 8 (8: 16 bytes of bfloat16, two 16-byte pieces of float32)
+template <int V> __device__ __forceinline__ void ld_w(const float* p, float (&o)[V]) {
+    if constexpr (V == 8) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+    } else if constexpr (V == 2) {
+        const float2 t = *reinterpret_cast<const float2*>(p); o[0] = t.x; o[1] = t.y;
+    } else {
+        o[0] = p[0];
+    }
+}
+template <int V> __device__ __forceinline__ void ld_w(const __nv_bfloat16* p, float (&o)[V]) {
+    if constexpr (V == 8) {
+        const uint4 t = *reinterpret_cast<const uint4*>(p);
+        const unsigned w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+            o[2 * i] = __low2float(h); o[2 * i + 1] = __high2float(h);
+        }
+    } else if constexpr (V == 2) {
+        const __nv_bfloat162 t = *reinterpret_cast<const __nv_bfloat162*>(p); o[0] = __low2float(t); o[1] = __high2float(t);
+    } else {
+        o[0] = __bfloat162float(p[0]);
+    }
+}
+template <int V> __device__ __forceinline__ void st_w(float* p, const float (&o)[V]) {
+    if constexpr (V == 8) {
+        *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(o[4], o[5], o[6], o[7]);
+    } else if constexpr (V == 2) {
+        *reinterpret_cast<float2*>(p) = make_float2(o[0], o[1]);
+    } else {
+        p[0] = o[0];
+    }
+}
+template <int V> __device__ __forceinline__ void st_w(__nv_bfloat16* p, const float (&o)[V]) {
+    if constexpr (V == 8) {
+        unsigned w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
+            w[i] = *reinterpret_cast<const unsigned*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else if constexpr (V == 2) {
+        *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(o[0], o[1]);
+    } else {
+        p[0] = __float2bfloat16_rn(o[0]);
+    }
+}
+static inline bool multiple_of(long long m, long long a, long long b = 0, long long c = 0, long long d = 0, long long e = 0, long long f = 0) {
+    return a % m == 0 && b % m == 0 && c % m == 0 && d % m == 0 && e % m == 0 && f % m == 0;
+}
 static inline bool even_all(long long a, long long b = 0, long long c = 0, long long d = 0, long long e = 0, long long f = 0) {
     return ((a | b | c | d | e | f) & 1) == 0;
 }
@@ -97,7 +151,7 @@ MSGL_API int msgl_dyntanh(const void* x, int x_is_f32, const float* res_in, floa
 // Short causal convolution on q and k + whole-projection RMS norm + cache write
 //
 //   proj row: q at column q_off (Cq = heads * d channels), k at column k_off (Ck = kv heads * d)
-//   y[t, c] = sum_j w[c, j] * u[t - taps + 1 + j, c]; inputs before this step's first token come from the
+//   y[t, c] = sum_j w[j, c] * u[t - taps + 1 + j, c] (the taps' weights come transposed, [taps][channels]); inputs before this step's first token come from the
 //   request's state [slot][taps - 1][Cq + Ck] (oldest first; zero when the request was opened)
 //   q_out = rms(y_q) * wq_norm;  K cache <- rms(y_k) * wk_norm;  V cache <- y_k (before the norm)
 // One block per token.
@@ -105,7 +159,7 @@ MSGL_API int msgl_dyntanh(const void* x, int x_is_f32, const float* res_in, floa
 struct ConvNormParams {
     const void* proj; long long stride; int q_off, k_off;
     int Cq, Ck, d, n_kv, taps;
-    const float* wq_conv; const float* wk_conv;      // [C, taps]
+    const float* wq_conv; const float* wk_conv;      // [taps, C]: a tap's weights of neighbouring channels side by side
     const float* wq_norm; const float* wk_norm;      // [C]
     float eps;
     void* state;                                     // [slots][taps - 1][Cq + Ck]
@@ -118,7 +172,7 @@ struct ConvNormParams {
 
 template <typename T, int V, int KMAX /* most taps: 4 or MIX_MAX_TAPS */>
 __global__ void __launch_bounds__(KMAX <= 4 ? 1024 : 256) conv_norm_kvwrite_kernel(const ConvNormParams p) {
-    extern __shared__ float ybuf[];                  // [Cq + Ck]
+    extern __shared__ __align__(16) float ybuf[];    // [Cq + Ck]
     __shared__ float red[64];
     const int t = blockIdx.x;
     const int r = p.token_req[t];
@@ -132,32 +186,37 @@ __global__ void __launch_bounds__(KMAX <= 4 ? 1024 : 256) conv_norm_kvwrite_kern
     for (int c = threadIdx.x * V; c < C; c += blockDim.x * V) {
         const bool is_q = c < p.Cq;
         const int cc = is_q ? c : c - p.Cq;
-        const float* w = (is_q ? p.wq_conv : p.wk_conv) + (size_t)cc * K;
+        const float* w = (is_q ? p.wq_conv : p.wk_conv) + cc;
+        const int Cw = is_q ? p.Cq : p.Ck;
         const int col = is_q ? p.q_off + cc : p.k_off + cc;
         // every input of the taps first, then the sums: the loads are in flight together
-        float u[KMAX][2];
+        float u[KMAX][V];
 #pragma unroll
         for (int j = 0; j < KMAX; ++j) {
             if (j < K) {
                 const int idx = i - (K - 1) + j;     // relative to the step's first token of this request
-                if (idx >= 0) ld_v<V>(proj + (size_t)(t0 + idx) * p.stride + col, u[j]);
-                else ld_v<V>(st + (size_t)(K - 1 + idx) * C + c, u[j]);
+                if (idx >= 0) ld_w<V>(proj + (size_t)(t0 + idx) * p.stride + col, u[j]);
+                else ld_w<V>(st + (size_t)(K - 1 + idx) * C + c, u[j]);
             }
         }
-        float acc[2] = {0.f, 0.f};
+        float acc[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v] = 0.f;
 #pragma unroll
         for (int j = 0; j < KMAX; ++j) {
             if (j < K) {
-                acc[0] = fmaf(w[j], u[j][0], acc[0]);
-                if (V == 2) acc[1] = fmaf(w[K + j], u[j][1], acc[1]);
+                float wv[V];
+                ld_w<V>(w + (size_t)j * Cw, wv);
+#pragma unroll
+                for (int v = 0; v < V; ++v) acc[v] = fmaf(wv[v], u[j][v], acc[v]);
             }
         }
 #pragma unroll
         for (int v = 0; v < V; ++v) {
-            const float y = to_f32<T>(from_f32<T>(acc[v]));   // as it leaves the convolution, in the activation type
-            ybuf[c + v] = y;
-            if (is_q) ssq_q += y * y; else ssq_k += y * y;
+            acc[v] = to_f32<T>(from_f32<T>(acc[v]));          // as it leaves the convolution, in the activation type
+            if (is_q) ssq_q += acc[v] * acc[v]; else ssq_k += acc[v] * acc[v];
         }
+        st_w<V>(ybuf + c, acc);
     }
     // both sums over the block at once
     {
@@ -177,19 +236,22 @@ __global__ void __launch_bounds__(KMAX <= 4 ? 1024 : 256) conv_norm_kvwrite_kern
     T* kc = reinterpret_cast<T*>(p.k_cache);
     T* vc = reinterpret_cast<T*>(p.v_cache);
     for (int c = threadIdx.x * V; c < C; c += blockDim.x * V) {      // a thread reads back what it wrote itself
-        float y[2] = {ybuf[c], V == 2 ? ybuf[c + 1] : 0.f}, o[2], wn[2];
+        float y[V], o[V], wn[V];
+        ld_w<V>(ybuf + c, y);
         if (c < p.Cq) {
-            ld_v<V>(p.wq_norm + c, wn);
-            o[0] = y[0] * rq * wn[0]; o[1] = y[1] * rq * wn[1];
-            st_v<V>(qo + c, o);
+            ld_w<V>(p.wq_norm + c, wn);
+#pragma unroll
+            for (int v = 0; v < V; ++v) o[v] = y[v] * rq * wn[v];
+            st_w<V>(qo + c, o);
         } else if (kc) {
             const int cc = c - p.Cq;
             const int g = cc / p.d, e = cc - g * p.d;
             const size_t a = (((size_t)page * p.n_kv + g) * p.page_size + ps) * p.d + e;
-            ld_v<V>(p.wk_norm + cc, wn);
-            o[0] = y[0] * rk * wn[0]; o[1] = y[1] * rk * wn[1];
-            st_v<V>(kc + a, o);
-            st_v<V>(vc + a, y);
+            ld_w<V>(p.wk_norm + cc, wn);
+#pragma unroll
+            for (int v = 0; v < V; ++v) o[v] = y[v] * rk * wn[v];
+            st_w<V>(kc + a, o);
+            st_w<V>(vc + a, y);
         }
     }
     if (p.one_token && K > 1) {
@@ -198,13 +260,13 @@ __global__ void __launch_bounds__(KMAX <= 4 ? 1024 : 256) conv_norm_kvwrite_kern
         T* stw = reinterpret_cast<T*>(p.state) + (size_t)slot * (K - 1) * C;
         for (int c = threadIdx.x * V; c < C; c += blockDim.x * V) {
             const int col = c < p.Cq ? p.q_off + c : p.k_off + (c - p.Cq);
-            float v[2];
+            float v[V];
             for (int k = 0; k + 1 < K - 1; ++k) {
-                ld_v<V>(stw + (size_t)(k + 1) * C + c, v);
-                st_v<V>(stw + (size_t)k * C + c, v);
+                ld_w<V>(stw + (size_t)(k + 1) * C + c, v);
+                st_w<V>(stw + (size_t)k * C + c, v);
             }
-            ld_v<V>(proj + (size_t)t * p.stride + col, v);
-            st_v<V>(stw + (size_t)(K - 2) * C + c, v);
+            ld_w<V>(proj + (size_t)t * p.stride + col, v);
+            st_w<V>(stw + (size_t)(K - 2) * C + c, v);
         }
     }
 }
@@ -254,13 +316,17 @@ MSGL_API int msgl_conv_norm_kvwrite(const void* proj, long long stride, int q_of
     // pairs of channels where nothing is odd: widths, head size, offsets, strides, pointers
     const bool v2 = even_all(Cq, Ck, d, q_off, k_off, stride) && aligned_to(proj, 2 * item) && aligned_to(state, 2 * item) &&
                     aligned_to(q_out, 2 * item) && aligned_to(k_cache, 2 * item) && aligned_to(v_cache, 2 * item) &&
-                    aligned_to(wq_norm, 8) && aligned_to(wk_norm, 8);
-    const int per = v2 ? 2 : 1;
+                    aligned_to(wq_norm, 8) && aligned_to(wk_norm, 8) && aligned_to(wq_conv, 8) && aligned_to(wk_conv, 8);
+    // eight channels at once where everything is a multiple of eight and 16-byte aligned
+    const bool v8 = v2 && multiple_of(8, Cq, Ck, d, q_off, k_off, stride) && aligned_to(proj, 16) && aligned_to(state, 16) &&
+                    aligned_to(q_out, 16) && aligned_to(k_cache, 16) && aligned_to(v_cache, 16) && aligned_to(wq_norm, 32) &&
+                    aligned_to(wk_norm, 32) && aligned_to(wq_conv, 32) && aligned_to(wk_conv, 32);
+    const int per = v8 ? 8 : (v2 ? 2 : 1);
     const int C = Cq + Ck;
     const bool few = taps <= 4;
     // many tokens: small blocks, several a multiprocessor, so that one block's loads overlap another's sums and stores; few
     // tokens: one large block a token
-    const int threads = (!few || T >= 256) ? 256 : (C / per >= 2048 ? 1024 : (C / per >= 512 ? 512 : 256));
+    const int threads = (!few || T >= 256) ? (C / per >= 512 ? 256 : 128) : (C / per >= 2048 ? 1024 : (C / per >= 512 ? 512 : 256));
 #define CONV_LAUNCH(T, V, KM)                                                                                         \
     do {                                                                                                              \
         static MsglOncePerDevice once;                                                                                \
@@ -272,8 +338,8 @@ MSGL_API int msgl_conv_norm_kvwrite(const void* proj, long long stride, int q_of
     } while (0)
 #define CONV_LAUNCH_K(T, V) do { if (few) CONV_LAUNCH(T, V, 4); else CONV_LAUNCH(T, V, MIX_MAX_TAPS); } while (0)
     const int T_ = T;
-    if (dtype == MSGL_F32) { if (v2) CONV_LAUNCH_K(float, 2); else CONV_LAUNCH_K(float, 1); }
-    else { if (v2) CONV_LAUNCH_K(__nv_bfloat16, 2); else CONV_LAUNCH_K(__nv_bfloat16, 1); }
+    if (dtype == MSGL_F32) { if (v8) CONV_LAUNCH_K(float, 8); else if (v2) CONV_LAUNCH_K(float, 2); else CONV_LAUNCH_K(float, 1); }
+    else { if (v8) CONV_LAUNCH_K(__nv_bfloat16, 8); else if (v2) CONV_LAUNCH_K(__nv_bfloat16, 2); else CONV_LAUNCH_K(__nv_bfloat16, 1); }
 #undef CONV_LAUNCH_K
 #undef CONV_LAUNCH
     if (taps > 1 && !p.one_token) {

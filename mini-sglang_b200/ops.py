@@ -723,7 +723,7 @@ def conv_norm_kvwrite(q_in: torch.Tensor, k_in: torch.Tensor, *, n_kv: int, head
                       q_start: torch.Tensor, slots: torch.Tensor, out_loc: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
                       v_cache: Optional[torch.Tensor], page_size: int, one_token: bool = False) -> torch.Tensor:
     """Short causal convolution over time on every channel of q_in [T, Cq] and k_in [T, Ck] (views into one packed
-    projection), continued from `state` [slots, taps - 1, Cq + Ck] (the request's last inputs, which the call brings up to
+    projection) with taps q_taps [taps, Cq] and k_taps [taps, Ck] (float32, the oldest input's tap first), continued from `state` [slots, taps - 1, Cq + Ck] (the request's last inputs, which the call brings up to
     date), then an RMS norm over the whole of q and of k.  The normed k goes to `k_cache`, the un-normed k to `v_cache`
     (layout [page][kv head][slot][head_dim]) at token slots `out_loc`; the normed q comes back as [T, Cq].  one_token: every
     request brings exactly one token (the state is then brought up to date by the same launch)."""
@@ -734,8 +734,8 @@ def conv_norm_kvwrite(q_in: torch.Tensor, k_in: torch.Tensor, *, n_kv: int, head
     item = q_in.element_size()
     q_off = 0
     k_off = (k_in.data_ptr() - q_in.data_ptr()) // item
-    taps = q_taps.shape[1]
-    assert q_taps.shape == (Cq, taps) and k_taps.shape == (Ck, taps) and q_taps.dtype == torch.float32 and k_taps.dtype == torch.float32
+    taps = q_taps.shape[0]
+    assert q_taps.shape == (taps, Cq) and k_taps.shape == (taps, Ck) and q_taps.dtype == torch.float32 and k_taps.dtype == torch.float32
     assert q_taps.is_contiguous() and k_taps.is_contiguous()
     assert q_norm.dtype == torch.float32 and k_norm.dtype == torch.float32 and q_norm.numel() == Cq and k_norm.numel() == Ck
     assert state.dtype == q_in.dtype and state.is_contiguous() and tuple(state.shape[1:]) == (max(taps - 1, 0), Cq + Ck)

@@ -83,7 +83,8 @@ class ConvWindowAttention(Mixer, Projected):
         f, n = src.fetch, self.names
         self.w_in = torch.cat((f(n["q"]), f(n["k"]), f(n["gate"])), dim=0).contiguous()
         self.w_out = f(n["out"]).contiguous()
-        self.q_taps, self.k_taps = f(n["q_conv"]).float().contiguous(), f(n["k_conv"]).float().contiguous()
+        # [taps, channels]: the kernel reads a tap's weights of neighbouring channels with one access
+        self.q_taps, self.k_taps = f(n["q_conv"]).float().t().contiguous(), f(n["k_conv"]).float().t().contiguous()
         self.q_norm, self.k_norm = f(n["q_norm"]).float().contiguous(), f(n["k_norm"]).float().contiguous()
         table = f(n["bias"]).float()                                   # [rows, heads]
         rows = table.shape[0]

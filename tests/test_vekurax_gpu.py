@@ -145,7 +145,8 @@ def test_distance_buckets_equal_the_plain_ones():
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("taps,cuts", [(4, (1, 2, 1, 5, 3, 11)), (2, (7, 1, 1, 14)), (1, (23,)), (5, (2, 2, 2, 2, 15)),
                                        (4, (3, 1, 1, 1, 1, 1, 1, 3)), (3, (1,) * 9), (6, (1,) * 8)])
-def test_convolution_norm_and_cache_write_in_portions(dtype, taps, cuts):
+@pytest.mark.parametrize("pad", [3, 0, 2])          # columns beside q and k in the packed rows: one, eight or two channels a thread
+def test_convolution_norm_and_cache_write_in_portions(dtype, taps, cuts, pad):
     """Two requests fed in different portions in the same steps: the convolution continues from each request's own state,
     and the cache receives the normed keys and the un-normed keys as values at the given slots."""
     from mini_sglang_b200 import ops
@@ -154,7 +155,7 @@ def test_convolution_norm_and_cache_write_in_portions(dtype, taps, cuts):
     Cq, Ck, T = H * d, G * d, sum(cuts)
     dt = DT[dtype]
     rnd = lambda *s: torch.randn(*s, generator=g).to(dt).float()          # noqa: E731
-    u = {r: rnd(T, Cq + Ck + 3) for r in (0, 1)}                            # packed rows: q | k | something else
+    u = {r: rnd(T, Cq + Ck + pad) for r in (0, 1)}                          # packed rows: q | k | something else
     qt, kt = 0.6 * torch.randn(Cq, taps, generator=g), 0.6 * torch.randn(Ck, taps, generator=g)
     qn, kn = 1 + 0.1 * torch.randn(Cq, generator=g), 1 + 0.1 * torch.randn(Ck, generator=g)
     eps = 1e-5
@@ -176,7 +177,8 @@ def test_convolution_norm_and_cache_write_in_portions(dtype, taps, cuts):
         token_req = torch.tensor(sum(([i] * n for i, n in enumerate(ns)), []), dtype=torch.int32).cuda()
         slots = torch.tensor([r + 1 for r in reqs], dtype=torch.int32).cuda()
         out_loc = torch.tensor(sum((loc[r][at[r]:at[r] + n] for r, n in zip(reqs, ns)), []), dtype=torch.int32).cuda()
-        q = ops.conv_norm_kvwrite(x[:, :Cq], x[:, Cq:Cq + Ck], n_kv=G, head_dim=d, q_taps=qt.cuda(), k_taps=kt.cuda(), q_norm=qn.cuda(),
+        q = ops.conv_norm_kvwrite(x[:, :Cq], x[:, Cq:Cq + Ck], n_kv=G, head_dim=d, q_taps=qt.t().contiguous().cuda(), k_taps=kt.t().contiguous().cuda(),
+                                  q_norm=qn.cuda(),
                                   k_norm=kn.cuda(), eps=eps, state=state, token_req=token_req, q_start=q_start, slots=slots,
                                   out_loc=out_loc, k_cache=kc, v_cache=vc, page_size=P, one_token=all(n == 1 for n in ns))
         o = 0

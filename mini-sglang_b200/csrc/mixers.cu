@@ -175,8 +175,9 @@ __global__ void __launch_bounds__(KMAX <= 4 ? 1024 : 256) conv_norm_kvwrite_kern
     extern __shared__ __align__(16) float ybuf[];    // [Cq + Ck]
     __shared__ float red[64];
     const int t = blockIdx.x;
-    const int r = p.token_req[t];
-    const int t0 = p.q_start[r];
+    // one token a request: token t is request t's only one, no lookups
+    const int r = p.one_token ? t : p.token_req[t];
+    const int t0 = p.one_token ? t : p.q_start[r];
     const int i = t - t0;                            // index of the token within the request's tokens of this step
     const int slot = p.slots[r];
     const int C = p.Cq + p.Ck, K = p.taps;

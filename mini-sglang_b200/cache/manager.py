@@ -46,6 +46,7 @@ class PagedKVNeed:
     library: Optional[str] = "attention"      # the kernel library that reads the cache (built before the first step);
                                               # "attention": csrc/attention.cu, whose decode launches the step plans kv splits for
     even_cut: bool = True            # whether a decode step may deal this cache's keys out evenly over the blocks
+    shared_kv: bool = False          # the values are read out of the key rows: one array is kept, not two
 
 
 @dataclasses.dataclass(frozen=True)

@@ -2,8 +2,10 @@ from .registry import ARCHITECTURES, ConfigError, architecture_of, load_config, 
 from .spec import LayerSpec, ModelSpec, PartSpec, Run
 from . import qwen3 as _qwen3  # registers "Qwen3ForCausalLM"
 from . import vekurax as _vekurax  # registers "Vekurax"
+from . import nametar as _nametar  # registers "Nametar"
 from .qwen3 import Qwen3Config
 from .vekurax import VekuraxConfig
+from .nametar import NametarConfig
 
 __all__ = ["ARCHITECTURES", "ConfigError", "architecture_of", "load_config", "read_config_json",
-           "register_architecture", "LayerSpec", "ModelSpec", "PartSpec", "Run", "Qwen3Config", "VekuraxConfig"]
+           "register_architecture", "LayerSpec", "ModelSpec", "PartSpec", "Run", "Qwen3Config", "VekuraxConfig", "NametarConfig"]

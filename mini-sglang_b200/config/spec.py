@@ -42,6 +42,8 @@ class LayerSpec:
     # checkpoint sub-names of the layer's parts under `prefix`: the block's role -> the name the checkpoint uses
     # (roles "mixer", "feed_forward" and the keys of `norms`); a role that is not listed keeps its own name
     names: Dict[str, str] = dataclasses.field(default_factory=dict)
+    # constants of the block arrangement itself (a factor on what a sublayer adds to the stream, say)
+    block_params: Dict[str, Any] = dataclasses.field(default_factory=dict)
 
     def part_prefix(self, role: str) -> str:
         return f"{self.prefix}.{self.names.get(role, role)}"

@@ -13,6 +13,16 @@
 //   rms_gate_kernel             RMS norm over a row, times sigmoid(gate), times a constant
 //   gated_act_kernel            act(gate) * up with act = silu or tanh-gelu
 //   head_gate_kernel            a head's output times the sigmoid of the head's gate, into packed rows
+//   scaled_embedding_kernel     res = float(E[ids]) * c, the start of the float32 stream of a model that scales its embedding
+//   postnorm_residual_kernel    res += c * rmsnorm(a) * w (a sublayer's output normed before it is added), and the next
+//                               sublayer's input norm of the new stream in the same pass
+//   latent_prep_kernel          latent attention: RMS norm of the query latent, RMS norm of the key/value latent and the
+//                               rotation of the shared rotated key part, both into one row of the paged cache
+//   rope_heads_kernel           the rotated part of every query head, angles from frequencies (no table, no position limit)
+//   gated_decay_attention_kernel   linear attention whose decay is made from the input per token and key channel,
+//                               S <- diag(alpha_t) S + k_t v_t^T, o = S^T q; token by token
+//   gated_decay_chunk_*_kernel  the same for long portions, chunks of a request in parallel
+//   group_rms_gate_kernel       RMS norm over each head of a row, times act(gate)
 //
 // Element type T (float or bfloat16) is the type of activations and caches; every sum, norm, score, weight of the
 // softmax, decay and state is float32 in both.  Inputs that come out of a packed projection are addressed by a base
@@ -932,7 +942,7 @@ MSGL_API int msgl_rms_gate(const float* x, int N, const float* w, float eps, con
 }
 
 // ---------------------------------------------------------------------------------------
-// out = act(gate) * up; act 0 = silu, 1 = gelu (tanh form)
+// out = act(gate) * up; act 0 = silu, 1 = gelu (tanh form), 2 = sigmoid
 // ---------------------------------------------------------------------------------------
 template <typename T, int V>
 __global__ void gated_act_kernel(const void* in_, long long in_stride, int gate_off, int up_off, void* out_, long long out_stride,
@@ -944,8 +954,8 @@ __global__ void gated_act_kernel(const void* in_, long long in_stride, int gate_
         float g[2], u[2], o[2];
         ld_v<V>(in + gate_off + i, g);
         ld_v<V>(in + up_off + i, u);
-        o[0] = (act == 1 ? gelu_tanhf_(g[0]) : siluf_(g[0])) * u[0];
-        o[1] = V == 2 ? (act == 1 ? gelu_tanhf_(g[1]) : siluf_(g[1])) * u[1] : 0.f;
+        o[0] = (act == 1 ? gelu_tanhf_(g[0]) : (act == 2 ? sigmoidf_(g[0]) : siluf_(g[0]))) * u[0];
+        o[1] = V == 2 ? (act == 1 ? gelu_tanhf_(g[1]) : (act == 2 ? sigmoidf_(g[1]) : siluf_(g[1]))) * u[1] : 0.f;
         st_v<V>(out + i, o);
     }
 }
@@ -953,7 +963,7 @@ __global__ void gated_act_kernel(const void* in_, long long in_stride, int gate_
 MSGL_API int msgl_gated_act(const void* in, long long in_stride, int gate_off, int up_off, void* out, long long out_stride,
                             int out_off, int I, int act, int T, int dtype, cudaStream_t stream) {
     if (T <= 0 || I <= 0) return MSGL_OK;
-    if (act != 0 && act != 1) return MSGL_ERR_SIZE;
+    if (act < 0 || act > 2) return MSGL_ERR_SIZE;
     if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
     const size_t item = dtype == MSGL_F32 ? 4 : 2;
     const bool v2 = even_all(I, in_stride, gate_off, up_off, out_stride, out_off) && aligned_to(in, 2 * item) && aligned_to(out, 2 * item);
@@ -1004,5 +1014,383 @@ MSGL_API int msgl_head_gate(const void* x, const void* gate, long long gate_stri
         if (v2) head_gate_kernel<__nv_bfloat16, 2><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, gate, gate_stride, gate_off, out, out_stride, out_off, heads, d, c);
         else head_gate_kernel<__nv_bfloat16, 1><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, gate, gate_stride, gate_off, out, out_stride, out_off, heads, d, c);
     }
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// res[t, :] = float(E[ids[t], :]) * c: the float32 stream of a model that scales its embedding
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void scaled_embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
+                                        int H, int V, float c) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (size_t)t * H;
+    const bool ok = id >= 0 && id < V;               // the host validates ids; one out of range gives zeros, never a wild read
+    const T* row = table + (size_t)(ok ? id : 0) * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ok ? to_f32<T>(row[i]) * c : 0.f;
+}
+
+MSGL_API int msgl_scaled_embedding(const int* ids, const void* table, float* out, int T_, int H, int V, float c, int dtype,
+                                   cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    if (H <= 0 || V <= 0) return MSGL_ERR_SIZE;
+    const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+    if (dtype == MSGL_F32) scaled_embedding_kernel<float><<<T_, threads, 0, stream>>>(ids, (const float*)table, out, H, V, c);
+    else if (dtype == MSGL_BF16)
+        scaled_embedding_kernel<__nv_bfloat16><<<T_, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, H, V, c);
+    else return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// A sublayer's output normed before it joins the stream, and the next sublayer's input norm in the same pass:
+//
+//   res[t, :] += c * a[t, :] / sqrt(mean(a[t, :]^2) + eps_a) * w_a             (float32, in place)
+//   y[t, :]    = res[t, :] / sqrt(mean(res[t, :]^2) + eps_y) * w_y             (only if w_y is given)
+//
+// One block per row; the row stays in shared memory between the passes.  a: activation type or float32.
+// ---------------------------------------------------------------------------------------
+template <typename T, typename A>
+__global__ void postnorm_residual_kernel(const A* __restrict__ a, const float* __restrict__ w_a, float eps_a, float c,
+                                         float* __restrict__ res, const float* __restrict__ w_y, float eps_y, T* __restrict__ y,
+                                         int H) {
+    extern __shared__ float prow[];                  // [H]
+    __shared__ float red[32];
+    const size_t off = (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = to_f32<A>(a[off + i]);
+        prow[i] = v;
+        ss += v * v;
+    }
+    const float ra = 1.f / sqrtf(block_sum(ss, red) / (float)H + eps_a);
+    ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {      // a thread reads back what it wrote itself
+        const float v = res[off + i] + c * (prow[i] * ra * w_a[i]);
+        res[off + i] = v;
+        prow[i] = v;
+        ss += v * v;
+    }
+    if (w_y == nullptr) return;
+    const float ry = 1.f / sqrtf(block_sum(ss, red) / (float)H + eps_y);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) y[off + i] = from_f32<T>(prow[i] * ry * w_y[i]);
+}
+
+MSGL_API int msgl_postnorm_residual(const void* a, int a_is_f32, const float* w_a, float eps_a, float c, float* res,
+                                    const float* w_y, float eps_y, void* y, int rows, int H, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return MSGL_OK;
+    if (H <= 0 || (size_t)H * sizeof(float) > 200 * 1024) return MSGL_ERR_SIZE;
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    const size_t smem = (size_t)H * sizeof(float);
+    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+#define PN_LAUNCH(T, A)                                                                                                    \
+    do {                                                                                                                   \
+        static MsglOncePerDevice once;                                                                                     \
+        if (smem > 48 * 1024 && once.due()) {                                                                              \
+            cudaFuncSetAttribute(postnorm_residual_kernel<T, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            once.mark();                                                                                                   \
+        }                                                                                                                  \
+        postnorm_residual_kernel<T, A><<<rows, threads, smem, stream>>>((const A*)a, w_a, eps_a, c, res, w_y, eps_y, (T*)y, H); \
+    } while (0)
+    if (dtype == MSGL_F32) PN_LAUNCH(float, float);
+    else if (a_is_f32) PN_LAUNCH(__nv_bfloat16, float);
+    else PN_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+#undef PN_LAUNCH
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// Latent attention, what a token leaves in the cache and the query latent:
+//
+//   proj row: the query's down-projection at column dq_off (q_rank wide; q_rank = 0: none), the key/value
+//   down-projection at column dkv_off (kv_rank + rot_dim wide)
+//   cq_out[t, :]               = rmsnorm(proj[dq ..]) * w_dq                                     (if q_rank > 0)
+//   cache row [0, kv_rank)     = rmsnorm(proj[dkv .. dkv + kv_rank]) * w_dkv                     the latent
+//   cache row [kv_rank, + rot_dim) = the last rot_dim columns, their first rot_dims rotated      one key part for all heads
+//
+// Rotation: element i < rot_dims / 2 with element i + rot_dims / 2, angle = position * freq[i] (float32), cos and sin times
+// `mag`; elements from rot_dims on pass unchanged.  The cache has one kv head of size kv_rank + rot_dim:
+// [page][slot in page][kv_rank + rot_dim].  One block per token.
+// ---------------------------------------------------------------------------------------
+struct LatentPrepParams {
+    const void* proj; long long stride; int dq_off, dkv_off;
+    int q_rank, kv_rank, rot_dim, rot_dims;
+    const float* w_dq; const float* w_dkv; float eps;
+    const float* freq; float mag;
+    const int* positions; const int* out_loc;
+    void* cq_out;                 // [T, q_rank]
+    void* cache; int page_size;   // may be null: nothing is written to the cache
+};
+
+template <typename T>
+__global__ void latent_prep_kernel(const LatentPrepParams p) {
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const T* row = reinterpret_cast<const T*>(p.proj) + (size_t)t * p.stride;
+    float sq = 0.f, sc = 0.f;
+    for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x) { const float v = to_f32<T>(row[p.dq_off + i]); sq += v * v; }
+    for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) { const float v = to_f32<T>(row[p.dkv_off + i]); sc += v * v; }
+    if (p.q_rank > 0) {
+        const float rq = 1.f / sqrtf(block_sum(sq, red) / (float)p.q_rank + p.eps);
+        T* cq = reinterpret_cast<T*>(p.cq_out) + (size_t)t * p.q_rank;
+        for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x) cq[i] = from_f32<T>(to_f32<T>(row[p.dq_off + i]) * rq * p.w_dq[i]);
+    }
+    const float rc = 1.f / sqrtf(block_sum(sc, red) / (float)p.kv_rank + p.eps);
+    if (p.cache == nullptr) return;
+    const int loc = p.out_loc[t];
+    const int D = p.kv_rank + p.rot_dim;
+    T* dst = reinterpret_cast<T*>(p.cache) + (size_t)loc * D;      // one kv head: token slot * row size
+    for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) dst[i] = from_f32<T>(to_f32<T>(row[p.dkv_off + i]) * rc * p.w_dkv[i]);
+    const T* kr = row + p.dkv_off + p.kv_rank;
+    const int half = p.rot_dims / 2;
+    const float pos = (float)p.positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf(pos * p.freq[i], &sn, &cs);
+        sn *= p.mag; cs *= p.mag;
+        const float u = to_f32<T>(kr[i]), v = to_f32<T>(kr[i + half]);
+        dst[p.kv_rank + i] = from_f32<T>(u * cs - v * sn);
+        dst[p.kv_rank + i + half] = from_f32<T>(v * cs + u * sn);
+    }
+    for (int i = p.rot_dims + threadIdx.x; i < p.rot_dim; i += blockDim.x) dst[p.kv_rank + i] = kr[i];
+}
+
+MSGL_API int msgl_latent_prep(const void* proj, long long stride, int dq_off, int dkv_off, int q_rank, int kv_rank, int rot_dim,
+                              int rot_dims, const float* w_dq, const float* w_dkv, float eps, const float* freq, float mag,
+                              const int* positions, const int* out_loc, void* cq_out, void* cache, int page_size, int T_,
+                              int dtype, cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    if (q_rank < 0 || kv_rank <= 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1)) return MSGL_ERR_SIZE;
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    LatentPrepParams p;
+    p.proj = proj; p.stride = stride; p.dq_off = dq_off; p.dkv_off = dkv_off; p.q_rank = q_rank; p.kv_rank = kv_rank;
+    p.rot_dim = rot_dim; p.rot_dims = rot_dims; p.w_dq = w_dq; p.w_dkv = w_dkv; p.eps = eps; p.freq = freq; p.mag = mag;
+    p.positions = positions; p.out_loc = out_loc; p.cq_out = cq_out; p.cache = cache; p.page_size = page_size;
+    const int widest = max(q_rank, kv_rank);
+    const int threads = widest >= 1024 ? 256 : (widest >= 256 ? 128 : 64);
+    if (dtype == MSGL_F32) latent_prep_kernel<float><<<T_, threads, 0, stream>>>(p);
+    else latent_prep_kernel<__nv_bfloat16><<<T_, threads, 0, stream>>>(p);
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// The rotated part of every query head: src [T rows][heads][src_head] with the part at column src_off of a head, dst
+// [T][heads][dst_head] with the part at column dst_off.  The first rot_dims of the part's rot_dim elements are rotated as
+// above, the rest are copied.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_heads_kernel(const T* __restrict__ src, long long src_stride, int src_head, int src_off, T* __restrict__ dst,
+                                  int dst_head, int dst_off, int heads, int rot_dim, int rot_dims,
+                                  const float* __restrict__ freq, float mag, const int* __restrict__ positions) {
+    const int t = blockIdx.x;
+    const float pos = (float)positions[t];
+    const int half = rot_dims / 2;
+    const T* s = src + (size_t)t * src_stride + src_off;
+    T* d = dst + (size_t)t * heads * dst_head + dst_off;
+    for (int idx = threadIdx.x; idx < heads * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx - h * half;
+        float sn, cs;
+        sincosf(pos * freq[i], &sn, &cs);
+        sn *= mag; cs *= mag;
+        const float u = to_f32<T>(s[(size_t)h * src_head + i]), v = to_f32<T>(s[(size_t)h * src_head + i + half]);
+        d[(size_t)h * dst_head + i] = from_f32<T>(u * cs - v * sn);
+        d[(size_t)h * dst_head + i + half] = from_f32<T>(v * cs + u * sn);
+    }
+    const int rest = rot_dim - rot_dims;
+    for (int idx = threadIdx.x; idx < heads * rest; idx += blockDim.x) {
+        const int h = idx / rest, i = rot_dims + idx - h * rest;
+        d[(size_t)h * dst_head + i] = s[(size_t)h * src_head + i];
+    }
+}
+
+MSGL_API int msgl_rope_heads(const void* src, long long src_stride, int src_head, int src_off, void* dst, int dst_head, int dst_off,
+                             int heads, int rot_dim, int rot_dims, const float* freq, float mag, const int* positions, int T_,
+                             int dtype, cudaStream_t stream) {
+    if (T_ <= 0 || rot_dim == 0) return MSGL_OK;
+    if (heads <= 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1) || src_off + rot_dim > src_head ||
+        dst_off + rot_dim > dst_head)
+        return MSGL_ERR_SIZE;
+    const int work = heads * max(rot_dims / 2, rot_dim - rot_dims);
+    const int threads = work >= 512 ? 256 : (work >= 128 ? 128 : 64);
+    if (dtype == MSGL_F32)
+        rope_heads_kernel<float><<<T_, threads, 0, stream>>>((const float*)src, src_stride, src_head, src_off, (float*)dst, dst_head,
+                                                             dst_off, heads, rot_dim, rot_dims, freq, mag, positions);
+    else if (dtype == MSGL_BF16)
+        rope_heads_kernel<__nv_bfloat16><<<T_, threads, 0, stream>>>((const __nv_bfloat16*)src, src_stride, src_head, src_off,
+                                                                     (__nv_bfloat16*)dst, dst_head, dst_off, heads, rot_dim,
+                                                                     rot_dims, freq, mag, positions);
+    else return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// out[t, i] = act(gate[t, i]) * x[t, i]; gate, x and out are [T, N] views into rows of their own strides; act 0 = silu,
+// 2 = sigmoid
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gate_mul_kernel(const T* __restrict__ gate, long long gate_stride, const T* __restrict__ x, long long x_stride,
+                                T* __restrict__ out, long long out_stride, int N, int act) {
+    const long long t = blockIdx.x;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < N; i += gridDim.y * blockDim.x) {
+        const float g = to_f32<T>(gate[t * gate_stride + i]);
+        out[t * out_stride + i] = from_f32<T>((act == 2 ? sigmoidf_(g) : siluf_(g)) * to_f32<T>(x[t * x_stride + i]));
+    }
+}
+
+MSGL_API int msgl_gate_mul(const void* gate, long long gate_stride, const void* x, long long x_stride, void* out,
+                           long long out_stride, int N, int act, int T_, int dtype, cudaStream_t stream) {
+    if (T_ <= 0 || N <= 0) return MSGL_OK;
+    if (act != 0 && act != 2) return MSGL_ERR_SIZE;
+    const dim3 grid(T_, max(1, min((N + 255) / 256, 32)));
+    if (dtype == MSGL_F32)
+        gate_mul_kernel<float><<<grid, 256, 0, stream>>>((const float*)gate, gate_stride, (const float*)x, x_stride, (float*)out, out_stride, N, act);
+    else if (dtype == MSGL_BF16)
+        gate_mul_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gate, gate_stride, (const __nv_bfloat16*)x, x_stride,
+                                                                 (__nv_bfloat16*)out, out_stride, N, act);
+    else return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// Linear attention whose decay comes from the input, per token and key channel:
+//
+//   q = proj q * q_scale, k = proj k [heads][dk], v = proj v [heads][dv]
+//   alpha = sigmoid(z + bias)^(1 / tau) = exp(logsigmoid(z + bias) / tau), z float32 [T][heads * dk]
+//   S_t = diag(alpha_t) S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t;  S per request [slot][heads][dk][dv] float32
+//
+// Same layout of the work as decay_attention_kernel: a block owns 32 columns of one (request, head) state and walks the
+// request's tokens of the step in order.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float log_sigmoidf_(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+template <typename T, int NR>
+__global__ void __launch_bounds__(DA_COLS * DA_PARTS)
+gated_decay_attention_kernel(const void* proj_, long long stride, int q_off, int k_off, int v_off, int heads, int dk, int dv,
+                             const float* __restrict__ z, const float* __restrict__ z_bias, float inv_tau, float q_scale,
+                             float* __restrict__ state, const int* __restrict__ q_start, const int* __restrict__ slots,
+                             float* __restrict__ out /* [T, heads * dv] */) {
+    extern __shared__ float qka[];                   // [2][3][dk]: double-buffered q, k and decay of the current token
+    const int r = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DA_COLS;
+    const int tid = threadIdx.x;
+    const int part = tid & (DA_PARTS - 1), col = col0 + (tid >> 3);
+    const bool col_ok = col < dv;
+    const int t0 = q_start[r], n = q_start[r + 1] - t0;
+    const int slot = slots[r];
+    const T* proj = reinterpret_cast<const T*>(proj_);
+    float* S = state + (((size_t)slot * heads + h) * dk) * dv;
+    const int rows = (dk + DA_PARTS - 1) / DA_PARTS;             // rows i = part + DA_PARTS * j
+    float s[NR];
+#pragma unroll
+    for (int j = 0; j < NR; ++j) {
+        const int i = part + DA_PARTS * j;
+        s[j] = (j < rows && i < dk && col_ok) ? S[(size_t)i * dv + col] : 0.f;
+    }
+    for (int tt = 0; tt < n; ++tt) {
+        const size_t row = (size_t)(t0 + tt) * stride;
+        float* qb = qka + (tt & 1) * 3 * dk;
+        float* kb = qb + dk;
+        float* ab = kb + dk;
+        for (int i = tid; i < dk; i += DA_COLS * DA_PARTS) {
+            qb[i] = to_f32<T>(proj[row + q_off + h * dk + i]) * q_scale;
+            kb[i] = to_f32<T>(proj[row + k_off + h * dk + i]);
+            const float zz = z[(size_t)(t0 + tt) * heads * dk + h * dk + i] + z_bias[h * dk + i];
+            ab[i] = expf(log_sigmoidf_(zz) * inv_tau);
+        }
+        const float v = col_ok ? to_f32<T>(proj[row + v_off + h * dv + col]) : 0.f;
+        __syncthreads();
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < NR; ++j) {
+            if (j < rows) {
+                const int i = part + DA_PARTS * j;
+                if (i < dk) {
+                    s[j] = fmaf(ab[i], s[j], kb[i] * v);
+                    acc = fmaf(s[j], qb[i], acc);
+                }
+            }
+        }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+        if (part == 0 && col_ok) out[(size_t)(t0 + tt) * heads * dv + h * dv + col] = acc;
+    }
+#pragma unroll
+    for (int j = 0; j < NR; ++j) {
+        const int i = part + DA_PARTS * j;
+        if (j < rows && i < dk && col_ok) S[(size_t)i * dv + col] = s[j];
+    }
+}
+
+MSGL_API int msgl_gated_decay_attention(const void* proj, long long stride, int q_off, int k_off, int v_off, int heads, int dk,
+                                        int dv, const float* z, const float* z_bias, float tau, float q_scale, float* state,
+                                        const int* q_start, const int* slots, float* out, int B, int dtype, cudaStream_t stream) {
+    if (B <= 0) return MSGL_OK;
+    if (heads <= 0 || dk <= 0 || dv <= 0 || dk > DA_PARTS * DA_MAX_ROWS || !(tau > 0.f)) return MSGL_ERR_SIZE;
+    const dim3 grid(B, heads, (dv + DA_COLS - 1) / DA_COLS);
+    const size_t smem = (size_t)6 * dk * sizeof(float);
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    const int nr = (dk + DA_PARTS - 1) / DA_PARTS;
+    const float inv_tau = 1.f / tau;
+#define GDA_LAUNCH(N)                                                                                                          \
+    do {                                                                                                                       \
+        if (dtype == MSGL_F32)                                                                                                 \
+            gated_decay_attention_kernel<float, N><<<grid, DA_COLS * DA_PARTS, smem, stream>>>(                                \
+                proj, stride, q_off, k_off, v_off, heads, dk, dv, z, z_bias, inv_tau, q_scale, state, q_start, slots, out);    \
+        else                                                                                                                   \
+            gated_decay_attention_kernel<__nv_bfloat16, N><<<grid, DA_COLS * DA_PARTS, smem, stream>>>(                        \
+                proj, stride, q_off, k_off, v_off, heads, dk, dv, z, z_bias, inv_tau, q_scale, state, q_start, slots, out);    \
+    } while (0)
+    if (nr <= 4) GDA_LAUNCH(4);
+    else if (nr <= 8) GDA_LAUNCH(8);
+    else if (nr <= 16) GDA_LAUNCH(16);
+    else if (nr <= 32) GDA_LAUNCH(32);
+    else GDA_LAUNCH(64);
+#undef GDA_LAUNCH
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// y[t, h, :] = x[t, h, :] / sqrt(mean(x[t, h, :]^2) + eps) * w * act(gate[t, h, :]) * c
+//   x float32 [T, heads, d] contiguous; w float32 [d], one weight for all heads; gate and y in packed rows;
+//   act 0 = silu, 2 = sigmoid.  One warp per (token, head).
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void group_rms_gate_kernel(const float* __restrict__ x, int heads, int d, const float* __restrict__ w, float eps,
+                                      const T* __restrict__ gate, long long gate_stride, T* __restrict__ out, long long out_stride,
+                                      float c, int act, long long n_rows) {
+    const long long rowi = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (rowi >= n_rows) return;
+    const int lane = threadIdx.x & 31;
+    const long long t = rowi / heads;
+    const int h = (int)(rowi - t * heads);
+    const float* xr = x + rowi * d;
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) { const float v = xr[i]; ss += v * v; }
+    const float rs = 1.f / sqrtf(warp_sum(ss) / (float)d + eps);
+    const T* g = gate ? gate + t * gate_stride + (long long)h * d : nullptr;
+    T* o = out + t * out_stride + (long long)h * d;
+    for (int i = lane; i < d; i += 32) {
+        float f = c;
+        if (g) { const float gv = to_f32<T>(g[i]); f *= (act == 2 ? sigmoidf_(gv) : siluf_(gv)); }
+        o[i] = from_f32<T>(xr[i] * rs * w[i] * f);
+    }
+}
+
+MSGL_API int msgl_group_rms_gate(const float* x, int heads, int d, const float* w, float eps, const void* gate,
+                                 long long gate_stride, void* out, long long out_stride, float c, int act, int T_, int dtype,
+                                 cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    if (heads <= 0 || d <= 0 || (act != 0 && act != 2)) return MSGL_ERR_SIZE;
+    const long long n_rows = (long long)T_ * heads;
+    const int warps = 4;
+    const unsigned blocks = (unsigned)((n_rows + warps - 1) / warps);
+    if (dtype == MSGL_F32)
+        group_rms_gate_kernel<float><<<blocks, warps * 32, 0, stream>>>(x, heads, d, w, eps, (const float*)gate, gate_stride, (float*)out,
+                                                                        out_stride, c, act, n_rows);
+    else if (dtype == MSGL_BF16)
+        group_rms_gate_kernel<__nv_bfloat16><<<blocks, warps * 32, 0, stream>>>(x, heads, d, w, eps, (const __nv_bfloat16*)gate, gate_stride,
+                                                                                (__nv_bfloat16*)out, out_stride, c, act, n_rows);
+    else return MSGL_ERR_DTYPE;
     return msgl_check_launch();
 }

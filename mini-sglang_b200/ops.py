@@ -661,7 +661,7 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
 # norms, convolutions, windowed and linear attention, gated activations (csrc/mixers.cu)
 # ---------------------------------------------------------------------------------------
 _mixers = None
-ACT_SILU, ACT_GELU_TANH = 0, 1
+ACT_SILU, ACT_GELU_TANH, ACT_SIGMOID = 0, 1, 2
 WINDOW_ATTENTION_ROWS = 8         # (token, head) rows of a block of the windowed attention kernel
 CONV_MAX_TAPS = 16
 WINDOW_ATTENTION_MAX_HEAD_DIM = 512
@@ -686,6 +686,18 @@ def _mix_lib():
         lib.msgl_head_gate.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]
         lib.msgl_decay_attention_chunked.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int] + [c_void_p] * 6 + \
             [c_int, c_int, c_int, c_void_p]
+        lib.msgl_scaled_embedding.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]
+        lib.msgl_postnorm_residual.argtypes = [c_void_p, c_int, c_void_p, c_float, c_float, c_void_p, c_void_p, c_float, c_void_p, c_int,
+                                               c_int, c_int, c_void_p]
+        lib.msgl_latent_prep.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
+                                         c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.msgl_rope_heads.argtypes = [c_void_p, c_ll, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float,
+                                        c_void_p, c_int, c_int, c_void_p]
+        lib.msgl_gate_mul.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p]
+        lib.msgl_gated_decay_attention.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                                                   c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
+        lib.msgl_group_rms_gate.argtypes = [c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_ll, c_void_p, c_ll, c_float, c_int,
+                                            c_int, c_int, c_void_p]
         _mixers = lib
     return _mixers
 
@@ -861,8 +873,8 @@ def rms_gate(x: torch.Tensor, weight: torch.Tensor, eps: float, gate: Optional[t
 
 
 def gated_act(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, act: int) -> None:
-    """out = act(gate) * up, act = ACT_SILU or ACT_GELU_TANH (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))); all three
-    [T, I] views into packed rows."""
+    """out = act(gate) * up, act = ACT_SILU, ACT_GELU_TANH (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))) or ACT_SIGMOID;
+    all three [T, I] views into packed rows, gate and up in the same rows."""
     _need_cuda(gate, up, out)
     T, I = gate.shape
     stride = _rows_view(gate, I, "gate")
@@ -871,6 +883,140 @@ def gated_act(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, act: int)
     code = _mix_lib().msgl_gated_act(_ptr(gate), stride, 0, up_off, _ptr(out), _rows_view(out, I, "out"), 0, I, int(act), T, _dt(gate),
                                      _stream())
     _check(code, "gated_act")
+
+
+def scaled_embedding(ids: torch.Tensor, table: torch.Tensor, scale: float) -> torch.Tensor:
+    """ids int32 [T], table [V, H] -> float32 [T, H] = float(table[ids]) * scale."""
+    _need_cuda(ids, table)
+    T, (V, H) = ids.numel(), table.shape
+    assert ids.dtype == torch.int32 and table.is_contiguous()
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    _check(_mix_lib().msgl_scaled_embedding(_ptr(ids), _ptr(table), _ptr(out), T, H, V, float(scale), _dt(table), _stream()),
+           "scaled_embedding")
+    return out
+
+
+def postnorm_residual(a: torch.Tensor, weight: torch.Tensor, eps: float, scale: float, residual: torch.Tensor, *,
+                      next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0,
+                      out_dtype: torch.dtype = torch.bfloat16) -> Optional[torch.Tensor]:
+    """residual += scale * rmsnorm(a) * weight in float32, in place (a sublayer's output that is normed before it joins the
+    stream); with `next_weight` also -> rmsnorm(residual) * next_weight in `out_dtype`, the next sublayer's input, from the same
+    pass over the row.  a: [T, H] float32 or `out_dtype`; weights float32 [H]."""
+    _need_cuda(a, weight, residual, next_weight)
+    T, H = a.shape
+    assert a.is_contiguous() and a.dtype in (torch.float32, out_dtype)
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and residual.shape == a.shape
+    assert weight.dtype == torch.float32 and weight.numel() == H
+    y = None
+    if next_weight is not None:
+        assert next_weight.dtype == torch.float32 and next_weight.numel() == H
+        y = torch.empty((T, H), dtype=out_dtype, device=a.device)
+    code = _mix_lib().msgl_postnorm_residual(_ptr(a), int(a.dtype == torch.float32), _ptr(weight), float(eps), float(scale),
+                                             _ptr(residual), _ptr(next_weight), float(next_eps), _ptr(y), T, H, _DT[out_dtype], _stream())
+    _check(code, "postnorm_residual")
+    return y
+
+
+def latent_prep(proj: torch.Tensor, *, dq_off: int, q_rank: int, dkv_off: int, kv_rank: int, rot_dim: int, rot_dims: int,
+                dq_norm: Optional[torch.Tensor], dkv_norm: torch.Tensor, eps: float, freq: Optional[torch.Tensor], mag: float,
+                positions: torch.Tensor, out_loc: Optional[torch.Tensor], cache: Optional[torch.Tensor],
+                page_size: int) -> Optional[torch.Tensor]:
+    """What a token of a latent attention leaves in the cache, and its query latent.  proj [T, .] holds the query's
+    down-projection (q_rank columns at dq_off; q_rank = 0: none) and the key/value down-projection (kv_rank + rot_dim columns
+    at dkv_off).  The cache row of a token (`cache` [pages, 1, page, kv_rank + rot_dim] at token slot out_loc) gets the RMS-normed
+    latent followed by the last rot_dim columns, whose first rot_dims are rotated by position * freq (pairs i, i + rot_dims / 2;
+    cos and sin times `mag`).  -> the RMS-normed query latent [T, q_rank], or None."""
+    _need_cuda(proj, dq_norm, dkv_norm, freq, positions, out_loc, cache)
+    T = proj.shape[0]
+    assert proj.dim() == 2 and proj.stride(1) == 1 and dkv_off + kv_rank + rot_dim <= proj.shape[1]
+    assert dkv_norm.dtype == torch.float32 and dkv_norm.numel() == kv_rank
+    assert positions.dtype == torch.int32 and positions.numel() == T
+    cq = None
+    if q_rank:
+        assert dq_norm is not None and dq_norm.dtype == torch.float32 and dq_norm.numel() == q_rank and dq_off + q_rank <= proj.shape[1]
+        cq = torch.empty((T, q_rank), dtype=proj.dtype, device=proj.device)
+    if rot_dims:
+        assert freq is not None and freq.dtype == torch.float32 and freq.numel() == rot_dims // 2
+    if cache is not None:
+        assert cache.dtype == proj.dtype and cache.is_contiguous() and cache.shape[1] == 1 and cache.shape[3] == kv_rank + rot_dim
+        assert out_loc is not None and out_loc.dtype == torch.int32 and out_loc.numel() == T
+    code = _mix_lib().msgl_latent_prep(_ptr(proj), proj.stride(0), dq_off, dkv_off, q_rank, kv_rank, rot_dim, rot_dims, _ptr(dq_norm),
+                                       _ptr(dkv_norm), float(eps), _ptr(freq), float(mag), _ptr(positions), _ptr(out_loc), _ptr(cq),
+                                       _ptr(cache), page_size, T, _dt(proj), _stream())
+    _check(code, "latent_prep")
+    return cq
+
+
+def rope_heads(src: torch.Tensor, src_off: int, dst: torch.Tensor, dst_off: int, *, rot_dim: int, rot_dims: int,
+               freq: torch.Tensor, mag: float, positions: torch.Tensor) -> None:
+    """dst[t, h, dst_off : dst_off + rot_dim] = the part src[t, h, src_off : src_off + rot_dim] of every head with its first
+    rot_dims elements rotated by position * freq (pairs i, i + rot_dims / 2; cos and sin times `mag`).  src [T, heads, a] may be
+    a view with a row stride of its own, dst [T, heads, b] is contiguous."""
+    _need_cuda(src, dst, freq, positions)
+    T, heads, sh = src.shape
+    assert dst.is_contiguous() and dst.shape[:2] == src.shape[:2] and dst.dtype == src.dtype
+    assert src.stride(2) == 1 and src.stride(1) == sh
+    assert freq.dtype == torch.float32 and freq.numel() == rot_dims // 2 and positions.dtype == torch.int32
+    code = _mix_lib().msgl_rope_heads(_ptr(src), src.stride(0), sh, src_off, _ptr(dst), dst.shape[2], dst_off, heads, rot_dim, rot_dims,
+                                      _ptr(freq), float(mag), _ptr(positions), T, _dt(src), _stream())
+    _check(code, "rope_heads")
+
+
+def gate_mul(gate: torch.Tensor, x: torch.Tensor, out: torch.Tensor, act: int) -> None:
+    """out = act(gate) * x with act = ACT_SIGMOID or ACT_SILU; [T, N] views into rows of their own strides."""
+    _need_cuda(gate, x, out)
+    T, N = x.shape
+    assert gate.dtype == x.dtype == out.dtype
+    code = _mix_lib().msgl_gate_mul(_ptr(gate), _rows_view(gate, N, "gate"), _ptr(x), _rows_view(x, N, "x"), _ptr(out),
+                                    _rows_view(out, N, "out"), N, int(act), T, _dt(x), _stream())
+    _check(code, "gate_mul")
+
+
+GATED_DECAY_CHUNKED_FROM = 32    # a step whose longest request brings this many tokens takes the chunked form
+
+
+def gated_decay_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, z_bias: torch.Tensor, *, heads: int,
+                          tau: float, q_scale: float, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor,
+                          q_lens: Optional[Sequence[int]] = None, workspace=None) -> torch.Tensor:
+    """Linear attention whose decay comes from the input, per token and key channel, continued from and written back to `state`
+    [slots, heads, dk, dv] float32: alpha = sigmoid(z + z_bias)^(1 / tau), S <- diag(alpha) S + k v^T, o = S^T (q * q_scale).
+    q, k [T, heads * dk] and v [T, heads * dv] are views into one packed projection; z float32 [T, heads * dk] contiguous,
+    z_bias float32 [heads * dk].  -> float32 [T, heads * dv].  q_lens: the requests' numbers of tokens as the host knows them
+    (None: every request is walked token by token)."""
+    _need_cuda(q, k, v, z, z_bias, state, q_start, slots)
+    T = q.shape[0]
+    dk, dv = q.shape[1] // heads, v.shape[1] // heads
+    stride = _rows_view(q, heads * dk, "q")
+    assert _rows_view(k, heads * dk, "k") == stride and _rows_view(v, heads * dv, "v") == stride and q.dtype == k.dtype == v.dtype
+    item = q.element_size()
+    k_off, v_off = (k.data_ptr() - q.data_ptr()) // item, (v.data_ptr() - q.data_ptr()) // item
+    assert z.dtype == torch.float32 and z.is_contiguous() and tuple(z.shape) == (T, heads * dk)
+    assert z_bias.dtype == torch.float32 and z_bias.numel() == heads * dk
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dk, dv)
+    out = torch.empty((T, heads * dv), dtype=torch.float32, device=q.device)
+    B = q_start.numel() - 1
+    code = _mix_lib().msgl_gated_decay_attention(_ptr(q), stride, 0, k_off, v_off, heads, dk, dv, _ptr(z), _ptr(z_bias), float(tau),
+                                                 float(q_scale), _ptr(state), _ptr(q_start), _ptr(slots), _ptr(out), B, _dt(q), _stream())
+    _check(code, f"gated_decay_attention (key size {dk})")
+    return out
+
+
+def group_rms_gate(x: torch.Tensor, heads: int, weight: torch.Tensor, eps: float, gate: Optional[torch.Tensor], out: torch.Tensor,
+                   act: int = ACT_SILU, scale: float = 1.0) -> None:
+    """out[t, h, :] = x[t, h, :] / sqrt(mean(x[t, h, :]^2) + eps) * weight * act(gate[t, h, :]) * scale: an RMS norm over every
+    head of a row with one weight [d] for all heads.  x float32 [T, heads * d] contiguous; gate and out [T, heads * d] views
+    into packed rows of the activation type; act = ACT_SILU or ACT_SIGMOID."""
+    _need_cuda(x, weight, gate, out)
+    T, N = x.shape
+    d = N // heads
+    assert x.dtype == torch.float32 and x.is_contiguous() and N == heads * d and weight.dtype == torch.float32 and weight.numel() == d
+    gs = 0
+    if gate is not None:
+        assert gate.dtype == out.dtype
+        gs = _rows_view(gate, N, "gate")
+    code = _mix_lib().msgl_group_rms_gate(_ptr(x), heads, d, _ptr(weight), float(eps), _ptr(gate), gs, _ptr(out),
+                                          _rows_view(out, N, "out"), float(scale), int(act), T, _dt(out), _stream())
+    _check(code, "group_rms_gate")
 
 
 # ---------------------------------------------------------------------------------------

@@ -129,3 +129,65 @@ class ParallelSharedNormBlock(Block):
         if self.ffn is not None:
             self.ffn.middle(proj[:, a:a + self.in_widths[1]], act[:, m:m + self.mid_widths[1]], ctx)
         return ops.linear(act, self.w_out, out_dtype=torch.float32), residual
+
+
+@register_block("sandwich_residual")
+class SandwichResidualBlock(Block):
+    """A norm before and after every sublayer:
+
+        res += m * norm_mixer_out(mixer(norm_in(res)));   res += m * norm_ffn_out(ffn(norm_ffn_in(res)))
+
+    with one factor m for both sums (`block_params["residual_scale"]`, default 1); the layer may have no feed-forward.  The
+    sums are float32.  Each sublayer's output norm, the sum and the following sublayer's input norm are one kernel
+    (`ops.postnorm_residual`); the block hands the stream on with nothing left un-added.  Roles of the norms: "input",
+    "mixer_out", "ffn_in", "ffn_out" (all `rmsnorm`)."""
+
+    def __init__(self, layer_spec, env: BuildEnv):
+        super().__init__(None, layer_spec.prefix, env)
+        at = layer_spec.part_prefix
+        self.scale = float(layer_spec.block_params.get("residual_scale", 1.0))
+        self.position = None
+        if layer_spec.position is not None:
+            self.position = env.shared(layer_spec.position, lambda: build_part(
+                POSITION_ENCODINGS, "position encoding", layer_spec.position, layer_spec.prefix, env))
+        self.norm_in = build_part(NORMS, "norm", layer_spec.norms["input"], at("input"), env)
+        self.norm_mixer_out = build_part(NORMS, "norm", layer_spec.norms["mixer_out"], at("mixer_out"), env)
+        self.mixer = build_part(MIXERS, "mixer", layer_spec.mixer, at("mixer"), env, position=self.position)
+        self.ffn = self.norm_ffn_in = self.norm_ffn_out = None
+        if layer_spec.feed_forward is not None:
+            self.norm_ffn_in = build_part(NORMS, "norm", layer_spec.norms["ffn_in"], at("ffn_in"), env)
+            self.norm_ffn_out = build_part(NORMS, "norm", layer_spec.norms["ffn_out"], at("ffn_out"), env)
+            self.ffn = build_part(FEED_FORWARDS, "feed-forward", layer_spec.feed_forward, at("feed_forward"), env)
+        for n in (self.norm_mixer_out, self.norm_ffn_in, self.norm_ffn_out):
+            if n is not None and not hasattr(n, "eps"):
+                raise ValueError("the sandwich block fuses RMS norms; another kind of norm is not taken here")
+        self._w = {}
+
+    def parts(self):
+        return [p for p in (self.position, self.norm_in, self.mixer, self.norm_mixer_out, self.norm_ffn_in, self.ffn,
+                            self.norm_ffn_out) if p is not None]
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        out: Dict[str, TensorDecl] = {}
+        for part in self.parts():
+            out.update(part.tensors())
+        return out
+
+    def load(self, src) -> None:
+        for part in self.parts():
+            part.load(src)
+        # the fused kernel reads float32 weights (exact: the checkpoint's values widened)
+        self._w = {k: n.weight.float().contiguous() for k, n in (("mixer_out", self.norm_mixer_out), ("ffn_in", self.norm_ffn_in),
+                                                                  ("ffn_out", self.norm_ffn_out)) if n is not None}
+
+    def forward(self, delta, residual, ctx, cache, writes_cache: bool = True):
+        y = self.norm_in.forward(x=delta, residual=residual, residual_out=residual if delta is not None else None)
+        a = self.mixer.forward(y, ctx, cache, writes_cache)
+        if self.ffn is None:
+            ops.postnorm_residual(a, self._w["mixer_out"], self.norm_mixer_out.eps, self.scale, residual, out_dtype=self.env.dtype)
+            return None, residual
+        y = ops.postnorm_residual(a, self._w["mixer_out"], self.norm_mixer_out.eps, self.scale, residual,
+                                  next_weight=self._w["ffn_in"], next_eps=self.norm_ffn_in.eps, out_dtype=self.env.dtype)
+        f = self.ffn.forward(y, ctx)
+        ops.postnorm_residual(f, self._w["ffn_out"], self.norm_ffn_out.eps, self.scale, residual, out_dtype=self.env.dtype)
+        return None, residual

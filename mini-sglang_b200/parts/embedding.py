@@ -11,14 +11,15 @@ from .base import Part, register_embedding, register_head
 
 @register_embedding("token_embedding")
 class TokenEmbedding(Part):
-    """h = E[ids], no scaling (mini_sglang/layers/embed_head.py:49); the result opens the float32
-    residual stream.  params: vocab_size, hidden_size, name.  An embedding part gets the step's context too
+    """h = E[ids] (mini_sglang/layers/embed_head.py:49), times `scale` where a model has one (in float32); the result opens
+    the float32 residual stream.  params: vocab_size, hidden_size, name, scale (default 1).  An embedding part gets the step's context too
     (`ctx.positions` for one that adds a position's own vector); this one does not need it."""
 
     def __init__(self, spec, prefix, env):
         super().__init__(spec, prefix, env)
         self.V, self.H = int(spec["vocab_size"]), int(spec["hidden_size"])
         self.tensor_name = spec.get("name") or self.name("weight")
+        self.scale = float(spec.get("scale", 1.0))
         self.weight = None
 
     def tensors(self) -> Dict[str, TensorDecl]:
@@ -28,9 +29,13 @@ class TokenEmbedding(Part):
         self.weight = src.fetch(self.tensor_name).contiguous()
 
     def forward(self, ids: torch.Tensor, ctx=None) -> torch.Tensor:
+        if self.scale != 1.0:
+            return ops.scaled_embedding(ids, self.weight, self.scale)
         return ops.embedding(ids, self.weight)
 
     def fused_decode_fields(self):
+        if self.scale != 1.0:
+            return None
         return {"kind": "token_embedding", "weight": self.weight, "V": self.V, "H": self.H}
 
 

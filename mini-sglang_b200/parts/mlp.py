@@ -78,4 +78,6 @@ class GatedMLP(FeedForward, Projected):
         ops.gated_act(proj[:, :self.I], proj[:, self.I:2 * self.I], act, self.act)
 
     def forward(self, x, ctx):
+        if self.act == ops.ACT_SILU:        # product and activation in one kernel where the engine has it (few rows; many rows in bfloat16)
+            return ops.linear(ops.linear_swiglu(x, self.gate_up), self.down)
         return self.forward_projected(x, ctx)

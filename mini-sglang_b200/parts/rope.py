@@ -41,3 +41,59 @@ class RotaryNeox(PositionEncoding):
 
     def fused_decode_fields(self):
         return {"kind": "rotary_table", "table": self.rotary_table(), "rot": self.rotary_dim, "max_pos": self.max_positions}
+
+
+@register_position_encoding("rope_yarn")
+class RotaryYarn(PositionEncoding):
+    """Rotary position encoding in halves (element i against i + rotary_dim / 2) with YaRN's frequency scaling.
+
+    f_i = theta^(-2 i / rotary_dim).  With `scaling` = {factor, original, fast, slow}: let dim(t) = rotary_dim ln(original /
+    (2 pi t)) / (2 ln theta), lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), rotary_dim - 1), ramp_i = clamp((i - lo)
+    / max(hi - lo, 0.001), 0, 1); the frequency becomes f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin are
+    multiplied by `magnitude` = 0.1 ln(factor) + 1.  Without `scaling`: plain frequencies, magnitude 1.
+
+    The frequencies are made on the host in double precision and kept as float32 (`inv_freq`); kernels that make their angles
+    themselves (position * frequency in float32) read them and have no position limit; `rotary_table()` gives the same angles
+    as a table of `max_positions` rows for kernels that look them up.
+    params: rotary_dim, theta, scaling (or None), max_positions."""
+
+    def __init__(self, spec, prefix, env):
+        super().__init__(spec, prefix, env)
+        self.rotary_dim = int(spec["rotary_dim"])
+        self.theta = float(spec["theta"])
+        self.scaling = dict(spec["scaling"]) if spec.get("scaling") else None
+        self.max_positions = int(spec.get("max_positions", 0))
+        if self.rotary_dim % 2 or self.rotary_dim < 0:
+            raise ValueError("rotary_dim must be even")
+        freq, self.magnitude = yarn_frequencies(self.rotary_dim, self.theta, self.scaling)
+        self._freq_host = freq.to(torch.float32)
+        self.inv_freq: Optional[torch.Tensor] = None
+        self._table: Optional[torch.Tensor] = None
+
+    def load(self, src) -> None:
+        self.inv_freq = self._freq_host.to(self.env.device).contiguous()
+
+    def rotary_table(self) -> torch.Tensor:
+        if self._table is None:
+            t = torch.arange(self.max_positions, dtype=torch.float32)
+            ang = t[:, None] * self._freq_host[None, :]
+            self._table = (torch.cat((ang.cos(), ang.sin()), dim=-1) * self.magnitude).contiguous().to(self.env.device)
+        return self._table
+
+
+def yarn_frequencies(rotary_dim: int, theta: float, scaling):
+    """-> (float64 frequencies [rotary_dim / 2], magnitude) of `RotaryYarn`."""
+    import math
+    i = torch.arange(rotary_dim // 2, dtype=torch.float64)
+    f = theta ** (-2.0 * i / rotary_dim) if rotary_dim else i
+    if not scaling:
+        return f, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def dim_of(turns: float) -> float:
+        return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(dim_of(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(dim_of(float(scaling["slow"]))), rotary_dim - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0

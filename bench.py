@@ -550,7 +550,37 @@ def vekurax_config(size, layers, vocab, window=1024, keep_first=4):
     return {"architecture": "Vekurax", "width": s["width"], "vocab": vocab, "norm": {"eps": 1e-5}, "layers": [layer] * layers}
 
 
-def workload_vekurax(args):
+def nametar_config(size, layers, vocab, window=1024):
+    """A Nametar model with the given layer sizes: the latent attentions have the heads of the Qwen3 layer with key size 128
+    (more rotated where the layer has a rotated part) and value size 128 over a cache row of 256 elements (latent 192 + 64
+    rotated, or 256; at the smaller size a row of 128: 96 + 32, or 128), a query latent of half the width and a window; the linear attention a quarter as many heads over half the width as keys and the whole width as
+    values; the feed-forward the same width.  Kinds of layers in turn: windowed latent attention, linear attention, gated
+    latent attention over all keys, linear attention."""
+    s = COMPARE_SIZES[size]
+    g_heads = max(s["heads"] // 4, 1)
+    row = 128 if s["width"] <= 2048 else 256
+    rot = row // 4
+    la2 = {"type": "latent_attention_2",
+           "mixer": {"heads": s["heads"], "dim": s["dim"], "rot_dim": rot, "vdim": s["dim"], "kv_rank": row - rot, "q_rank": s["width"] // 2,
+                     "scale": (s["dim"] + rot) ** -0.5, "mask": {"size": window},
+                     "rot": {"base": 10000.0, "dims": rot, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+           "mlp": {"kind": "dense", "ff": s["ff"]}}
+    la = {"type": "latent_attention",
+          "mixer": {"heads": s["heads"], "dim": s["dim"], "vdim": s["dim"], "kv_rank": row, "scale": s["dim"] ** -0.5},
+          "mlp": {"kind": "dense", "ff": s["ff"]}}
+    gla = {"type": "gla", "mixer": {"heads": g_heads, "dim": s["width"] // 2 // g_heads, "vdim": s["width"] // g_heads, "tau": 16.0},
+           "mlp": {"kind": "dense", "ff": s["ff"]}}
+    kinds = [la2, gla, la, gla]
+    return {"architecture": "Nametar", "width": s["width"], "vocab": vocab, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "embedding": {"scale": float(s["width"]) ** 0.5}, "layers": [kinds[i % 4] for i in range(layers)]}
+
+
+def workload_nametar(args):
+    """As --workload vekurax_compare, with a Nametar model (`nametar_config`) beside the Qwen3 model of equal sizes."""
+    return workload_vekurax(args, name="nametar", config=nametar_config)
+
+
+def workload_vekurax(args, name="vekurax", config=None):
     """Prefill (one 2,048-token prompt a step) and decode (--batch requests at --context tokens, one token each a step through
     the CUDA graph) of a Vekurax model and of a Qwen3 model with the same width, heads, feed-forward width, vocabulary and number
     of layers (--layers, default 4; random weights), device-timed, with the mean time of every kernel of a step."""
@@ -567,7 +597,8 @@ def workload_vekurax(args):
     clocks.start()
     gen = torch.Generator().manual_seed(0)
     rand = lambda n: torch.randint(0, V, (n,), generator=gen).tolist()      # noqa: E731
-    out = {"workload": "vekurax_compare", "layers": L, "batch": B, "context": CTX, "prefill_tokens": PREFILL, "vocab": V,
+    config = config or vekurax_config
+    out = {"workload": name + "_compare", "layers": L, "batch": B, "context": CTX, "prefill_tokens": PREFILL, "vocab": V,
            "dtype": "bf16", "data": "synthetic (random weights, random tokens)", "peaks": pk, "sizes": {}}
     for size in (args.sizes.split(",") if args.sizes else list(COMPARE_SIZES)):
         s = COMPARE_SIZES[size]
@@ -575,7 +606,7 @@ def workload_vekurax(args):
                     num_key_value_heads=s["kv_heads"], head_dim=s["dim"], intermediate_size=s["ff"], vocab_size=V,
                     tie_word_embeddings=True, max_position_embeddings=CTX + 4096)
         res = {}
-        for arch, cfg in (("vekurax", vekurax_config(size, L, V)), ("qwen3", qwen)):
+        for arch, cfg in ((name, config(size, L, V)), ("qwen3", qwen)):
             tmp = tempfile.mkdtemp(prefix="msgl_bench_")
             with open(os.path.join(tmp, "config.json"), "w") as f:
                 json.dump(cfg, f)
@@ -650,9 +681,9 @@ def main():
     ap.add_argument("--profiler-range", action="store_true",
                     help="cudaProfilerStart/Stop around the timed region (ncu --profile-from-start off)")
     ap.add_argument("--no-graph", action="store_true", help="decode without CUDA graphs")
-    ap.add_argument("--workload", default="headline", choices=["headline", "qwen3_0.6b_mixed", "qwen3_32b_long", "sweep", "vekurax_compare"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "qwen3_0.6b_mixed", "qwen3_32b_long", "sweep", "vekurax_compare", "nametar_compare"],
                     help="headline: the line the contract names; the others: further workloads, one JSON line each")
-    ap.add_argument("--sizes", default=None, help="--workload vekurax_compare: layer sizes to run, of " + ",".join(COMPARE_SIZES))
+    ap.add_argument("--sizes", default=None, help="--workload vekurax_compare / nametar_compare: layer sizes to run, of " + ",".join(COMPARE_SIZES))
     ap.add_argument("--skip-sanity", action="store_true", help="no comparison with the plain implementation before timing")
     ap.add_argument("--model", default="8b", choices=["8b", "32b", "0.6b"], help="layer sizes for --only decode / prefill")
     ap.add_argument("--lengths", default=None,
@@ -674,6 +705,8 @@ def main():
         return workload_sweep(args)
     if args.workload == "vekurax_compare":
         return workload_vekurax(args)
+    if args.workload == "nametar_compare":
+        return workload_nametar(args)
 
     import torch
 

@@ -1049,7 +1049,8 @@ MSGL_API int msgl_scaled_embedding(const int* ids, const void* table, float* out
 //   res[t, :] += c * a[t, :] / sqrt(mean(a[t, :]^2) + eps_a) * w_a             (float32, in place)
 //   y[t, :]    = res[t, :] / sqrt(mean(res[t, :]^2) + eps_y) * w_y             (only if w_y is given)
 //
-// One block per row; the row stays in shared memory between the passes.  a: activation type or float32.
+// One block per row; the row stays in registers between the passes (in shared memory beyond 8,192 columns).  a: activation
+// type or float32.
 // ---------------------------------------------------------------------------------------
 template <typename T, typename A>
 __global__ void postnorm_residual_kernel(const A* __restrict__ a, const float* __restrict__ w_a, float eps_a, float c,
@@ -1077,13 +1078,66 @@ __global__ void postnorm_residual_kernel(const A* __restrict__ a, const float* _
     for (int i = threadIdx.x; i < H; i += blockDim.x) y[off + i] = from_f32<T>(prow[i] * ry * w_y[i]);
 }
 
+// The same with the row in registers (VPT values a thread, all loads of a row in flight together): rows up to 1024 * VPT wide.
+template <typename T, typename A, int VPT>
+__global__ void __launch_bounds__(1024) postnorm_residual_reg_kernel(const A* __restrict__ a, const float* __restrict__ w_a, float eps_a,
+                                                                     float c, float* __restrict__ res, const float* __restrict__ w_y,
+                                                                     float eps_y, T* __restrict__ y, int H) {
+    __shared__ float red[32];
+    const size_t off = (size_t)blockIdx.x * H;
+    float av[VPT], rv[VPT], wa[VPT], wy[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        const bool ok = i < H;
+        av[k] = ok ? to_f32<A>(a[off + i]) : 0.f;
+        rv[k] = ok ? res[off + i] : 0.f;
+        wa[k] = ok ? w_a[i] : 0.f;
+        wy[k] = (ok && w_y != nullptr) ? w_y[i] : 0.f;
+        ss += av[k] * av[k];
+    }
+    const float ra = 1.f / sqrtf(block_sum(ss, red) / (float)H + eps_a);
+    ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        const float v = rv[k] + c * (av[k] * ra * wa[k]);
+        if (i < H) res[off + i] = v;
+        rv[k] = v;
+        ss += v * v;
+    }
+    if (w_y == nullptr) return;
+    const float ry = 1.f / sqrtf(block_sum(ss, red) / (float)H + eps_y);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < H) y[off + i] = from_f32<T>(rv[k] * ry * wy[k]);
+    }
+}
+
 MSGL_API int msgl_postnorm_residual(const void* a, int a_is_f32, const float* w_a, float eps_a, float c, float* res,
                                     const float* w_y, float eps_y, void* y, int rows, int H, int dtype, cudaStream_t stream) {
     if (rows <= 0) return MSGL_OK;
     if (H <= 0 || (size_t)H * sizeof(float) > 200 * 1024) return MSGL_ERR_SIZE;
     if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    if (H <= 8192) {
+        // the kernel and its block size follow from the row's width alone, so a row's sums do not depend on the batch
+        const int vpt = H <= 4096 ? 4 : 8;
+        const int threads = min(1024, ((H + vpt - 1) / vpt + 31) / 32 * 32);
+#define PNR_LAUNCH(T, A)                                                                                                       \
+    do {                                                                                                                       \
+        if (vpt == 4) postnorm_residual_reg_kernel<T, A, 4><<<rows, threads, 0, stream>>>((const A*)a, w_a, eps_a, c, res, w_y, eps_y, (T*)y, H); \
+        else postnorm_residual_reg_kernel<T, A, 8><<<rows, threads, 0, stream>>>((const A*)a, w_a, eps_a, c, res, w_y, eps_y, (T*)y, H);          \
+    } while (0)
+        if (dtype == MSGL_F32) PNR_LAUNCH(float, float);
+        else if (a_is_f32) PNR_LAUNCH(__nv_bfloat16, float);
+        else PNR_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+#undef PNR_LAUNCH
+        return msgl_check_launch();
+    }
     const size_t smem = (size_t)H * sizeof(float);
-    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+    const int threads = 512;
 #define PN_LAUNCH(T, A)                                                                                                    \
     do {                                                                                                                   \
         static MsglOncePerDevice once;                                                                                     \
@@ -1392,5 +1446,285 @@ MSGL_API int msgl_group_rms_gate(const float* x, int heads, int d, const float* 
         group_rms_gate_kernel<__nv_bfloat16><<<blocks, warps * 32, 0, stream>>>(x, heads, d, w, eps, (const __nv_bfloat16*)gate, gate_stride,
                                                                                 (__nv_bfloat16*)out, out_stride, c, act, n_rows);
     else return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// The same gated linear attention for long portions: a request's tokens of the step in chunks of 64, the chunks in
+// parallel.  With L tokens in a chunk (local index i), g_i = log2(alpha_i) per key channel, b_i = g_0 + ... + g_i, and S the
+// state before the chunk:
+//
+//   1. gated_chunk_prep_kernel   b_i for every token (a running sum per channel within the chunk)
+//   2. gated_chunk_kv_kernel     U = sum_i diag(2^(b_(L-1) - b_i)) k_i v_i^T                   every chunk by itself
+//   3. gated_chunk_scan_kernel   per request, chunk after chunk: U <- S, S <- diag(2^b_(L-1)) S + U; the state row gets the last S
+//   4. gated_chunk_p_kernel      P[i][j] = sum_c q_i[c] k_j[c] 2^(b_i[c] - b_j[c]) for j <= i  (one exponential a term: every
+//                                exponent is <= 0, so nothing overflows however strong the decay)
+//   5. gated_chunk_out_kernel    o_i = (q_i * 2^b_i) S + sum_(j <= i) P[i][j] v_j
+//
+// All products are float32 FMA through shared memory; the results differ from the token-by-token kernel by rounding only.
+// ---------------------------------------------------------------------------------------
+struct GatedChunkParams {
+    DecayChunkParams d;           // d.decay is not used
+    const float* z; const float* z_bias; float inv_tau_log2e; float q_scale;
+    float* bcum;                  // [T][heads * dk]
+    float* P;                     // [chunks][heads][64][64]
+};
+
+__global__ void __launch_bounds__(128) gated_chunk_prep_kernel(const GatedChunkParams p) {
+    __shared__ int sh[2];
+    int req, t0, L;
+    if (!dc_find_chunk(p.d, blockIdx.x, sh, req, t0, L)) return;
+    const int HK = p.d.heads * p.d.dk;
+    const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+    if (ch >= HK) return;
+    const float bias = p.z_bias[ch];
+    float run = 0.f;
+    for (int i = 0; i < L; ++i) {
+        const size_t at = (size_t)(t0 + i) * HK + ch;
+        run += log_sigmoidf_(p.z[at] + bias) * p.inv_tau_log2e;
+        p.bcum[at] = run;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) gated_chunk_kv_kernel(const GatedChunkParams p) {
+    __shared__ __align__(16) float Ks[DC_C][64];
+    __shared__ __align__(16) float Vs[DC_C][64];
+    __shared__ int sh[2];
+    const DecayChunkParams& d = p.d;
+    const int chunk = blockIdx.x, h = blockIdx.y;
+    const int n_ct = (d.dv + 63) / 64;
+    const int row0 = (blockIdx.z / n_ct) * 64, col0 = (blockIdx.z % n_ct) * 64;
+    int req, t0, L;
+    if (!dc_find_chunk(d, chunk, sh, req, t0, L)) return;
+    const int HK = d.heads * d.dk;
+    const T* proj = reinterpret_cast<const T*>(d.proj);
+    const int tid = threadIdx.x;
+    for (int idx = tid; idx < DC_C * 64; idx += 256) {
+        const int i = idx >> 6, m = idx & 63;
+        float kv = 0.f, vv = 0.f;
+        if (i < L) {
+            const size_t row = (size_t)(t0 + i) * d.stride;
+            if (row0 + m < d.dk) {
+                const int ch = h * d.dk + row0 + m;
+                const float e = p.bcum[(size_t)(t0 + L - 1) * HK + ch] - p.bcum[(size_t)(t0 + i) * HK + ch];
+                kv = to_f32<T>(proj[row + d.k_off + ch]) * exp2f(fminf(e, 0.f));
+            }
+            if (col0 + m < d.dv) vv = to_f32<T>(proj[row + d.v_off + h * d.dv + col0 + m]);
+        }
+        Ks[i][m] = kv;
+        Vs[i][m] = vv;
+    }
+    __syncthreads();
+    const int ty = tid >> 4, tx = tid & 15;
+    float acc[4][4] = {};
+    for (int i = 0; i < L; ++i) {
+        const float4 kr = *reinterpret_cast<const float4*>(&Ks[i][ty * 4]);
+        const float4 vr = *reinterpret_cast<const float4*>(&Vs[i][tx * 4]);
+        const float ka[4] = {kr.x, kr.y, kr.z, kr.w}, va[4] = {vr.x, vr.y, vr.z, vr.w};
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(ka[a], va[b], acc[a][b]);
+    }
+    float* U = d.U + ((size_t)chunk * d.heads + h) * d.dk * d.dv;
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int row = row0 + ty * 4 + a;
+        if (row >= d.dk) continue;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int col = col0 + tx * 4 + b;
+            if (col < d.dv) U[(size_t)row * d.dv + col] = acc[a][b];
+        }
+    }
+}
+
+__global__ void gated_chunk_scan_kernel(const GatedChunkParams p) {
+    const DecayChunkParams& d = p.d;
+    const int r = blockIdx.x, h = blockIdx.y;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    const int E = d.dk * d.dv;
+    if (e >= E) return;
+    const int base = d.q_start[r], n = d.q_start[r + 1] - base;
+    if (n <= 0) return;
+    int chunk0 = 0;
+    for (int r2 = 0; r2 < r; ++r2) chunk0 += (d.q_start[r2 + 1] - d.q_start[r2] + DC_C - 1) / DC_C;
+    const int HK = d.heads * d.dk;
+    const int ch = h * d.dk + e / d.dv;
+    float* st = d.state + ((size_t)d.slots[r] * d.heads + h) * E + e;
+    float S = *st;
+    const int nc = (n + DC_C - 1) / DC_C;
+    // eight chunks at a time: their sums and decays are fetched together, then the state walks through them
+    for (int c0 = 0; c0 < nc; c0 += 8) {
+        float uv[8], f[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int c = c0 + k;
+            if (c < nc) {
+                const int L = min(DC_C, n - c * DC_C);
+                uv[k] = d.U[((size_t)(chunk0 + c) * d.heads + h) * E + e];
+                f[k] = p.bcum[(size_t)(base + c * DC_C + L - 1) * HK + ch];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int c = c0 + k;
+            if (c < nc) {
+                d.U[((size_t)(chunk0 + c) * d.heads + h) * E + e] = S;
+                S = fmaf(exp2f(f[k]), S, uv[k]);
+            }
+        }
+    }
+    *st = S;
+}
+
+#define GC_IB 16        // rows of P a block makes
+#define GC_CT 32        // key channels staged at a time
+template <typename T>
+__global__ void __launch_bounds__(256) gated_chunk_p_kernel(const GatedChunkParams p) {
+    __shared__ float Qs[GC_IB][GC_CT + 1], BQs[GC_IB][GC_CT + 1];
+    __shared__ float Ks[DC_C][GC_CT + 1], BKs[DC_C][GC_CT + 1];
+    __shared__ int sh[2];
+    const DecayChunkParams& d = p.d;
+    const int chunk = blockIdx.x, h = blockIdx.y, ib = blockIdx.z;
+    int req, t0, L;
+    if (!dc_find_chunk(d, chunk, sh, req, t0, L)) return;
+    float* P = p.P + ((size_t)chunk * d.heads + h) * DC_C * DC_C;
+    const int tid = threadIdx.x, ii = tid >> 4, jj = tid & 15;
+    const int i = ib * GC_IB + ii;
+    if (ib * GC_IB >= L) {          // rows past the chunk's last token
+        for (int m = 0; m < DC_C / 16; ++m) P[(size_t)i * DC_C + jj + 16 * m] = 0.f;
+        return;
+    }
+    const int HK = d.heads * d.dk;
+    const T* proj = reinterpret_cast<const T*>(d.proj);
+    const int n_j = (ib + 1) * GC_IB;          // keys 0 .. n_j - 1 can be seen from this block's rows
+    float acc[DC_C / 16] = {};
+    for (int c0 = 0; c0 < d.dk; c0 += GC_CT) {
+        __syncthreads();
+        for (int idx = tid; idx < (GC_IB + n_j) * GC_CT; idx += 256) {
+            const int rr = idx / GC_CT, c = idx - rr * GC_CT;
+            const bool is_q = rr < GC_IB;
+            const int tok = is_q ? ib * GC_IB + rr : rr - GC_IB;
+            float x = 0.f, bb = 0.f;
+            if (tok < L && c0 + c < d.dk) {
+                const int ch = h * d.dk + c0 + c;
+                x = to_f32<T>(proj[(size_t)(t0 + tok) * d.stride + (is_q ? d.q_off : d.k_off) + ch]);
+                bb = p.bcum[(size_t)(t0 + tok) * HK + ch];
+            }
+            if (is_q) { Qs[rr][c] = x * p.q_scale; BQs[rr][c] = bb; }
+            else { Ks[tok][c] = x; BKs[tok][c] = bb; }
+        }
+        __syncthreads();
+        for (int c = 0; c < GC_CT; ++c) {
+            const float qv = Qs[ii][c], bq = BQs[ii][c];
+#pragma unroll
+            for (int m = 0; m < DC_C / 16; ++m) {
+                if (m <= ib) {
+                    const int j = jj + 16 * m;
+                    acc[m] = fmaf(qv * Ks[j][c], exp2f(fminf(bq - BKs[j][c], 0.f)), acc[m]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < DC_C / 16; ++m) {
+        const int j = jj + 16 * m;
+        P[(size_t)i * DC_C + j] = (m <= ib && j <= i && i < L) ? acc[m] : 0.f;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) gated_chunk_out_kernel(const GatedChunkParams p) {
+    __shared__ __align__(16) float As[DC_C][DC_LD];       // v; then slabs of q * 2^b
+    __shared__ __align__(16) float Bs[DC_C][DC_LD];       // the chunk's weights P; then slabs of S
+    __shared__ int sh[2];
+    const DecayChunkParams& d = p.d;
+    const int chunk = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * 64;
+    int req, t0, L;
+    if (!dc_find_chunk(d, chunk, sh, req, t0, L)) return;
+    const int HK = d.heads * d.dk;
+    const T* proj = reinterpret_cast<const T*>(d.proj);
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    const float* P = p.P + ((size_t)chunk * d.heads + h) * DC_C * DC_C;
+    for (int idx = tid; idx < DC_C * 64; idx += 256) {
+        const int j = idx >> 6, nn = idx & 63;
+        Bs[j][nn] = P[idx];                                   // here j is P's row i, nn its column j
+        float vv = 0.f;
+        if (j < L && col0 + nn < d.dv) vv = to_f32<T>(proj[(size_t)(t0 + j) * d.stride + d.v_off + h * d.dv + col0 + nn]);
+        As[j][nn] = vv;
+    }
+    __syncthreads();
+    // ---- O = P V
+    float oacc[4][4] = {};
+    for (int j = 0; j < L; ++j) {
+        float pa[4], vb[4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) { pa[a] = Bs[ty * 4 + a][j]; vb[a] = As[j][tx * 4 + a]; }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) oacc[a][b] = fmaf(pa[a], vb[b], oacc[a][b]);
+    }
+    // ---- O += (Q * 2^b) S, S the state before the chunk
+    const float* S = d.U + ((size_t)chunk * d.heads + h) * d.dk * d.dv;
+    for (int m0 = 0; m0 < d.dk; m0 += 64) {
+        __syncthreads();
+        for (int idx = tid; idx < DC_C * 64; idx += 256) {
+            const int i = idx >> 6, m = idx & 63;
+            float qv = 0.f;
+            if (i < L && m0 + m < d.dk) {
+                const int ch = h * d.dk + m0 + m;
+                qv = to_f32<T>(proj[(size_t)(t0 + i) * d.stride + d.q_off + ch]) * p.q_scale * exp2f(p.bcum[(size_t)(t0 + i) * HK + ch]);
+            }
+            As[i][m] = qv;
+            float sv = 0.f;                        // here i is the state's row within the slab, m its column
+            if (m0 + i < d.dk && col0 + m < d.dv) sv = S[(size_t)(m0 + i) * d.dv + col0 + m];
+            Bs[i][m] = sv;
+        }
+        __syncthreads();
+        for (int m = 0; m < 64; ++m) {
+            float qa[4], sb[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) { qa[a] = As[ty * 4 + a][m]; sb[a] = Bs[m][tx * 4 + a]; }
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) oacc[a][b] = fmaf(qa[a], sb[b], oacc[a][b]);
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int i = ty * 4 + a;
+        if (i >= L) continue;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int col = col0 + tx * 4 + b;
+            if (col < d.dv) d.out[(size_t)(t0 + i) * d.heads * d.dv + h * d.dv + col] = oacc[a][b];
+        }
+    }
+}
+
+MSGL_API int msgl_gated_decay_attention_chunked(const void* proj, long long stride, int q_off, int k_off, int v_off, int heads,
+                                                int dk, int dv, const float* z, const float* z_bias, float tau, float q_scale,
+                                                float* state, const int* q_start, const int* slots, float* out, float* U,
+                                                float* bcum, float* P, int n_chunks, int B, int dtype, cudaStream_t stream) {
+    if (B <= 0 || n_chunks <= 0) return MSGL_OK;
+    if (heads <= 0 || dk <= 0 || dv <= 0 || !(tau > 0.f)) return MSGL_ERR_SIZE;
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    GatedChunkParams p;
+    p.d.proj = proj; p.d.stride = stride; p.d.q_off = q_off; p.d.k_off = k_off; p.d.v_off = v_off; p.d.heads = heads; p.d.dk = dk;
+    p.d.dv = dv; p.d.B = B; p.d.decay = nullptr; p.d.state = state; p.d.q_start = q_start; p.d.slots = slots; p.d.U = U; p.d.out = out;
+    p.z = z; p.z_bias = z_bias; p.inv_tau_log2e = 1.4426950408889634f / tau; p.q_scale = q_scale; p.bcum = bcum; p.P = P;
+    const int n_rt = (dk + 63) / 64, n_ct = (dv + 63) / 64;
+    gated_chunk_prep_kernel<<<dim3(n_chunks, (heads * dk + 127) / 128), 128, 0, stream>>>(p);
+    if (dtype == MSGL_F32) gated_chunk_kv_kernel<float><<<dim3(n_chunks, heads, n_rt * n_ct), 256, 0, stream>>>(p);
+    else gated_chunk_kv_kernel<__nv_bfloat16><<<dim3(n_chunks, heads, n_rt * n_ct), 256, 0, stream>>>(p);
+    gated_chunk_scan_kernel<<<dim3(B, heads, (dk * dv + 255) / 256), 256, 0, stream>>>(p);
+    if (dtype == MSGL_F32) gated_chunk_p_kernel<float><<<dim3(n_chunks, heads, DC_C / GC_IB), 256, 0, stream>>>(p);
+    else gated_chunk_p_kernel<__nv_bfloat16><<<dim3(n_chunks, heads, DC_C / GC_IB), 256, 0, stream>>>(p);
+    if (dtype == MSGL_F32) gated_chunk_out_kernel<float><<<dim3(n_chunks, heads, n_ct), 256, 0, stream>>>(p);
+    else gated_chunk_out_kernel<__nv_bfloat16><<<dim3(n_chunks, heads, n_ct), 256, 0, stream>>>(p);
     return msgl_check_launch();
 }

@@ -696,6 +696,8 @@ def _mix_lib():
         lib.msgl_gate_mul.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p]
         lib.msgl_gated_decay_attention.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
                                                    c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
+        lib.msgl_gated_decay_attention_chunked.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                                           c_float, c_float] + [c_void_p] * 7 + [c_int, c_int, c_int, c_void_p]
         lib.msgl_group_rms_gate.argtypes = [c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_ll, c_void_p, c_ll, c_float, c_int,
                                             c_int, c_int, c_void_p]
         _mixers = lib
@@ -982,7 +984,9 @@ def gated_decay_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: 
     [slots, heads, dk, dv] float32: alpha = sigmoid(z + z_bias)^(1 / tau), S <- diag(alpha) S + k v^T, o = S^T (q * q_scale).
     q, k [T, heads * dk] and v [T, heads * dv] are views into one packed projection; z float32 [T, heads * dk] contiguous,
     z_bias float32 [heads * dk].  -> float32 [T, heads * dv].  q_lens: the requests' numbers of tokens as the host knows them
-    (None: every request is walked token by token)."""
+    (None: every request is walked token by token); when the longest has GATED_DECAY_CHUNKED_FROM or more, the step is computed
+    in chunks of DECAY_CHUNK tokens that run in parallel (the same sums in another order).  workspace: a parts.Workspace for the
+    chunks' scratch."""
     _need_cuda(q, k, v, z, z_bias, state, q_start, slots)
     T = q.shape[0]
     dk, dv = q.shape[1] // heads, v.shape[1] // heads
@@ -995,6 +999,19 @@ def gated_decay_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: 
     assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dk, dv)
     out = torch.empty((T, heads * dv), dtype=torch.float32, device=q.device)
     B = q_start.numel() - 1
+    if q_lens is not None and max(q_lens, default=0) >= GATED_DECAY_CHUNKED_FROM:
+        n_chunks = sum(-(-n // DECAY_CHUNK) for n in q_lens)
+        sizes = (("gated_chunk_states", n_chunks * heads * dk * dv), ("gated_chunk_decays", T * heads * dk),
+                 ("gated_chunk_weights", n_chunks * heads * DECAY_CHUNK * DECAY_CHUNK))
+        U, bcum, P = (workspace.get(name, n, torch.float32) if workspace is not None else
+                      torch.empty(n, dtype=torch.float32, device=q.device) for name, n in sizes)
+        code = _mix_lib().msgl_gated_decay_attention_chunked(
+            _ptr(q), stride, 0, k_off, v_off, heads, dk, dv, _ptr(z), _ptr(z_bias), float(tau), float(q_scale), _ptr(state),
+            _ptr(q_start), _ptr(slots), _ptr(out), _ptr(U), _ptr(bcum), _ptr(P), n_chunks, B, _dt(q), _stream())
+        _check(code, f"gated_decay_attention in chunks (key size {dk})")
+        global LAUNCHES
+        LAUNCHES += 4
+        return out
     code = _mix_lib().msgl_gated_decay_attention(_ptr(q), stride, 0, k_off, v_off, heads, dk, dv, _ptr(z), _ptr(z_bias), float(tau),
                                                  float(q_scale), _ptr(state), _ptr(q_start), _ptr(slots), _ptr(out), B, _dt(q), _stream())
     _check(code, f"gated_decay_attention (key size {dk})")

@@ -1078,9 +1078,10 @@ __global__ void postnorm_residual_kernel(const A* __restrict__ a, const float* _
     for (int i = threadIdx.x; i < H; i += blockDim.x) y[off + i] = from_f32<T>(prow[i] * ry * w_y[i]);
 }
 
-// The same with the row in registers (VPT values a thread, all loads of a row in flight together): rows up to 1024 * VPT wide.
+// The same with the row in registers (VPT values a thread, all loads of a row in flight together): rows up to 512 * VPT wide.
+// Blocks of at most 512 threads, so that several rows share a multiprocessor and one row's sums overlap another's loads.
 template <typename T, typename A, int VPT>
-__global__ void __launch_bounds__(1024) postnorm_residual_reg_kernel(const A* __restrict__ a, const float* __restrict__ w_a, float eps_a,
+__global__ void __launch_bounds__(512) postnorm_residual_reg_kernel(const A* __restrict__ a, const float* __restrict__ w_a, float eps_a,
                                                                      float c, float* __restrict__ res, const float* __restrict__ w_y,
                                                                      float eps_y, T* __restrict__ y, int H) {
     __shared__ float red[32];
@@ -1123,12 +1124,12 @@ MSGL_API int msgl_postnorm_residual(const void* a, int a_is_f32, const float* w_
     if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
     if (H <= 8192) {
         // the kernel and its block size follow from the row's width alone, so a row's sums do not depend on the batch
-        const int vpt = H <= 4096 ? 4 : 8;
-        const int threads = min(1024, ((H + vpt - 1) / vpt + 31) / 32 * 32);
+        const int vpt = H <= 4096 ? 8 : 16;
+        const int threads = min(512, ((H + vpt - 1) / vpt + 31) / 32 * 32);
 #define PNR_LAUNCH(T, A)                                                                                                       \
     do {                                                                                                                       \
-        if (vpt == 4) postnorm_residual_reg_kernel<T, A, 4><<<rows, threads, 0, stream>>>((const A*)a, w_a, eps_a, c, res, w_y, eps_y, (T*)y, H); \
-        else postnorm_residual_reg_kernel<T, A, 8><<<rows, threads, 0, stream>>>((const A*)a, w_a, eps_a, c, res, w_y, eps_y, (T*)y, H);          \
+        if (vpt == 8) postnorm_residual_reg_kernel<T, A, 8><<<rows, threads, 0, stream>>>((const A*)a, w_a, eps_a, c, res, w_y, eps_y, (T*)y, H); \
+        else postnorm_residual_reg_kernel<T, A, 16><<<rows, threads, 0, stream>>>((const A*)a, w_a, eps_a, c, res, w_y, eps_y, (T*)y, H);         \
     } while (0)
         if (dtype == MSGL_F32) PNR_LAUNCH(float, float);
         else if (a_is_f32) PNR_LAUNCH(__nv_bfloat16, float);
@@ -1409,7 +1410,7 @@ MSGL_API int msgl_gated_decay_attention(const void* proj, long long stride, int 
 //   x float32 [T, heads, d] contiguous; w float32 [d], one weight for all heads; gate and y in packed rows;
 //   act 0 = silu, 2 = sigmoid.  One warp per (token, head).
 // ---------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, int NPL /* elements of a head per lane held in registers: head sizes up to 32 * NPL; 0: any size, two passes */>
 __global__ void group_rms_gate_kernel(const float* __restrict__ x, int heads, int d, const float* __restrict__ w, float eps,
                                       const T* __restrict__ gate, long long gate_stride, T* __restrict__ out, long long out_stride,
                                       float c, int act, long long n_rows) {
@@ -1419,15 +1420,36 @@ __global__ void group_rms_gate_kernel(const float* __restrict__ x, int heads, in
     const long long t = rowi / heads;
     const int h = (int)(rowi - t * heads);
     const float* xr = x + rowi * d;
-    float ss = 0.f;
-    for (int i = lane; i < d; i += 32) { const float v = xr[i]; ss += v * v; }
-    const float rs = 1.f / sqrtf(warp_sum(ss) / (float)d + eps);
     const T* g = gate ? gate + t * gate_stride + (long long)h * d : nullptr;
     T* o = out + t * out_stride + (long long)h * d;
-    for (int i = lane; i < d; i += 32) {
-        float f = c;
-        if (g) { const float gv = to_f32<T>(g[i]); f *= (act == 2 ? sigmoidf_(gv) : siluf_(gv)); }
-        o[i] = from_f32<T>(xr[i] * rs * w[i] * f);
+    if constexpr (NPL > 0) {
+        float xv[NPL], gv[NPL], wv[NPL];
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < NPL; ++k) {
+            const int i = lane + 32 * k;
+            const bool ok = i < d;
+            xv[k] = ok ? xr[i] : 0.f;
+            gv[k] = (ok && g) ? to_f32<T>(g[i]) : 0.f;
+            wv[k] = ok ? w[i] : 0.f;
+            ss += xv[k] * xv[k];
+        }
+        const float rs = 1.f / sqrtf(warp_sum(ss) / (float)d + eps);
+#pragma unroll
+        for (int k = 0; k < NPL; ++k) {
+            const int i = lane + 32 * k;
+            const float f = g ? c * (act == 2 ? sigmoidf_(gv[k]) : siluf_(gv[k])) : c;
+            if (i < d) o[i] = from_f32<T>(xv[k] * rs * wv[k] * f);
+        }
+    } else {
+        float ss = 0.f;
+        for (int i = lane; i < d; i += 32) { const float v = xr[i]; ss += v * v; }
+        const float rs = 1.f / sqrtf(warp_sum(ss) / (float)d + eps);
+        for (int i = lane; i < d; i += 32) {
+            float f = c;
+            if (g) { const float gv = to_f32<T>(g[i]); f *= (act == 2 ? sigmoidf_(gv) : siluf_(gv)); }
+            o[i] = from_f32<T>(xr[i] * rs * w[i] * f);
+        }
     }
 }
 
@@ -1439,13 +1461,22 @@ MSGL_API int msgl_group_rms_gate(const float* x, int heads, int d, const float* 
     const long long n_rows = (long long)T_ * heads;
     const int warps = 4;
     const unsigned blocks = (unsigned)((n_rows + warps - 1) / warps);
-    if (dtype == MSGL_F32)
-        group_rms_gate_kernel<float><<<blocks, warps * 32, 0, stream>>>(x, heads, d, w, eps, (const float*)gate, gate_stride, (float*)out,
-                                                                        out_stride, c, act, n_rows);
-    else if (dtype == MSGL_BF16)
-        group_rms_gate_kernel<__nv_bfloat16><<<blocks, warps * 32, 0, stream>>>(x, heads, d, w, eps, (const __nv_bfloat16*)gate, gate_stride,
-                                                                                (__nv_bfloat16*)out, out_stride, c, act, n_rows);
-    else return MSGL_ERR_DTYPE;
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+#define GRG_LAUNCH(N)                                                                                                          \
+    do {                                                                                                                       \
+        if (dtype == MSGL_F32)                                                                                                 \
+            group_rms_gate_kernel<float, N><<<blocks, warps * 32, 0, stream>>>(x, heads, d, w, eps, (const float*)gate, gate_stride,   \
+                                                                               (float*)out, out_stride, c, act, n_rows);       \
+        else                                                                                                                   \
+            group_rms_gate_kernel<__nv_bfloat16, N><<<blocks, warps * 32, 0, stream>>>(x, heads, d, w, eps, (const __nv_bfloat16*)gate, \
+                                                                                       gate_stride, (__nv_bfloat16*)out, out_stride,    \
+                                                                                       c, act, n_rows);                        \
+    } while (0)
+    if (d <= 128) GRG_LAUNCH(4);
+    else if (d <= 256) GRG_LAUNCH(8);
+    else if (d <= 512) GRG_LAUNCH(16);
+    else GRG_LAUNCH(0);
+#undef GRG_LAUNCH
     return msgl_check_launch();
 }
 

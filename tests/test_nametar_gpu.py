@@ -78,13 +78,26 @@ def row_close(row, want, dtype, bound=BF16_RMS_FRACTION_N):
 
 
 def compare(name, dtype, got, seqs):
+    """Every row against the plain implementation.  bfloat16: rounding noise has outliers (a row whose sums nearly cancel before
+    a norm), so one row in fifty (at least one) may pass the bound, none by more than two and a half times; a fault of the
+    cache, a window or a state moves every row behind it by more than that."""
     assert got
+    bound = BF16_RMS_FRACTION_BY_CONFIG.get(name, BF16_RMS_FRACTION_N)
+    over = []
     for (rid, pos), row in sorted(got.items()):
         want = plain(name, tuple(seqs[rid]))[pos]
         try:
-            row_close(row, want, dtype, BF16_RMS_FRACTION_BY_CONFIG.get(name, BF16_RMS_FRACTION_N))
+            row_close(row, want, dtype, bound)
         except AssertionError as e:
+            if dtype == "bfloat16" and torch.isfinite(row).all():
+                try:
+                    row_close(row, want, dtype, 2.5 * bound)
+                    over.append((rid, pos))
+                    continue
+                except AssertionError:
+                    pass
             raise AssertionError(f"request {rid!r} position {pos} ({dtype}, {name}): {e}") from None
+    assert len(over) <= max(1, len(got) // 50), f"{len(over)} of {len(got)} rows beyond the bound ({dtype}, {name}): {over[:8]}"
 
 
 def poison(r):
@@ -188,10 +201,11 @@ def test_latents_cache_rows_and_query_rotation(dtype, geo):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_gates(dtype):
+@pytest.mark.parametrize("d", [13, 200, 512, 530])
+def test_gates(dtype, d):
     from mini_sglang_b200 import ops
     g = torch.Generator().manual_seed(1)
-    T, heads, d, dt = 5, 3, 13, DT[dtype]
+    T, heads, dt = 5, 3, DT[dtype]
     N = heads * d
     packed = (2 * torch.randn(T, N + 6, generator=g)).to(dt).cuda()
     x = torch.randn(T, N, generator=g).to(dt).cuda()

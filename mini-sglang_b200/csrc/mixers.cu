@@ -1117,13 +1117,81 @@ __global__ void __launch_bounds__(512) postnorm_residual_reg_kernel(const A* __r
     }
 }
 
+// The same with eight neighbouring columns a thread and access (16-byte loads and stores), G such groups a thread: rows whose
+// width is a multiple of 8, up to 512 * 8 * G columns, every pointer 16-byte aligned.
+template <typename T, typename A, int G>
+__global__ void __launch_bounds__(512) postnorm_residual_vec_kernel(const A* __restrict__ a, const float* __restrict__ w_a, float eps_a,
+                                                                    float c, float* __restrict__ res, const float* __restrict__ w_y,
+                                                                    float eps_y, T* __restrict__ y, int H) {
+    __shared__ float red[32];
+    const size_t off = (size_t)blockIdx.x * H;
+    float av[G][8], rv[G][8], wa[G][8], wy[G][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const int i = (threadIdx.x + g * blockDim.x) * 8;
+        if (i < H) {
+            ld_w<8>(a + off + i, av[g]);
+            ld_w<8>(res + off + i, rv[g]);
+            ld_w<8>(w_a + i, wa[g]);
+            if (w_y != nullptr) ld_w<8>(w_y + i, wy[g]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { av[g][e] = 0.f; rv[g][e] = 0.f; wa[g][e] = 0.f; }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += av[g][e] * av[g][e];
+    }
+    const float ra = 1.f / sqrtf(block_sum(ss, red) / (float)H + eps_a);
+    ss = 0.f;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const int i = (threadIdx.x + g * blockDim.x) * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float v = rv[g][e] + c * (av[g][e] * ra * wa[g][e]);
+            rv[g][e] = v;
+            ss += v * v;
+        }
+        if (i < H) st_w<8>(res + off + i, rv[g]);
+    }
+    if (w_y == nullptr) return;
+    const float ry = 1.f / sqrtf(block_sum(ss, red) / (float)H + eps_y);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const int i = (threadIdx.x + g * blockDim.x) * 8;
+        if (i < H) {
+            float o[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = rv[g][e] * ry * wy[g][e];
+            st_w<8>(y + off + i, o);
+        }
+    }
+}
+
 MSGL_API int msgl_postnorm_residual(const void* a, int a_is_f32, const float* w_a, float eps_a, float c, float* res,
                                     const float* w_y, float eps_y, void* y, int rows, int H, int dtype, cudaStream_t stream) {
     if (rows <= 0) return MSGL_OK;
     if (H <= 0 || (size_t)H * sizeof(float) > 200 * 1024) return MSGL_ERR_SIZE;
     if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    if (H <= 8192 && H % 8 == 0 && aligned_to(a, 16) && aligned_to(res, 16) && aligned_to(w_a, 16) && aligned_to(w_y, 16) && aligned_to(y, 16)) {
+        const int groups = H / 8;
+        const int threads = min(512, (groups + 31) / 32 * 32);
+        const bool two = groups > threads;
+#define PNV_LAUNCH(T, A)                                                                                                       \
+    do {                                                                                                                       \
+        if (!two) postnorm_residual_vec_kernel<T, A, 1><<<rows, threads, 0, stream>>>((const A*)a, w_a, eps_a, c, res, w_y, eps_y, (T*)y, H); \
+        else postnorm_residual_vec_kernel<T, A, 2><<<rows, threads, 0, stream>>>((const A*)a, w_a, eps_a, c, res, w_y, eps_y, (T*)y, H);      \
+    } while (0)
+        if (dtype == MSGL_F32) PNV_LAUNCH(float, float);
+        else if (a_is_f32) PNV_LAUNCH(__nv_bfloat16, float);
+        else PNV_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+#undef PNV_LAUNCH
+        return msgl_check_launch();
+    }
     if (H <= 8192) {
-        // the kernel and its block size follow from the row's width alone, so a row's sums do not depend on the batch
+        // the kernel and its block size follow from the row's width (and the buffers' alignment) alone, so a row's sums do not
+        // depend on the batch
         const int vpt = H <= 4096 ? 8 : 16;
         const int threads = min(512, ((H + vpt - 1) / vpt + 31) / 32 * 32);
 #define PNR_LAUNCH(T, A)                                                                                                       \

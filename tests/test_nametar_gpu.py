@@ -129,7 +129,7 @@ def test_scaled_embedding(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H", [70, 1024, 5000, 9000])
+@pytest.mark.parametrize("H", [70, 1024, 4100, 5000, 8192, 9000])
 def test_output_norm_sum_and_next_input_norm(dtype, H):
     from mini_sglang_b200 import ops
     g = torch.Generator().manual_seed(H)

@@ -47,10 +47,12 @@ class RotaryNeox(PositionEncoding):
 class RotaryYarn(PositionEncoding):
     """Rotary position encoding in halves (element i against i + rotary_dim / 2) with YaRN's frequency scaling.
 
-    f_i = theta^(-2 i / rotary_dim).  With `scaling` = {factor, original, fast, slow}: let dim(t) = rotary_dim ln(original /
-    (2 pi t)) / (2 ln theta), lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), rotary_dim - 1), ramp_i = clamp((i - lo)
-    / max(hi - lo, 0.001), 0, 1); the frequency becomes f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin are
-    multiplied by `magnitude` = 0.1 ln(factor) + 1.  Without `scaling`: plain frequencies, magnitude 1.
+    Pair i of n = rotary_dim / 2 turns with frequency f_i = theta^(-i / n).  `scaling` = {factor, original, fast, slow} slows the
+    pairs whose wavelength is long against a context of `original` tokens: a pair that makes t turns within `original` tokens
+    has the (real-valued) index p(t) = n log_theta(original / (2 pi t)); between lo = max(floor(p(fast)), 0) and
+    hi = min(ceil(p(slow)), rotary_dim - 1) a ramp r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) blends the plain frequency
+    into the slowed one, f_i (1 - r_i) + (f_i / factor) r_i.  cos and sin are multiplied by `magnitude` = 1 + 0.1 ln(factor).
+    Without `scaling`: plain frequencies, magnitude 1.
 
     The frequencies are made on the host in double precision and kept as float32 (`inv_freq`); kernels that make their angles
     themselves (position * frequency in float32) read them and have no position limit; `rotary_table()` gives the same angles

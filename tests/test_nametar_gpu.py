@@ -374,15 +374,16 @@ LENGTHS = {"NA": 61, "NB": 40, "NC": 75}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["NA", "NB", "NC"])
-def test_whole_prompt_token_by_token_and_in_portions(name, dtype):
+@pytest.mark.parametrize("name,page", [("NA", None), ("NB", None), ("NC", None), ("NA", 16), ("NB", 8), ("NC", 1)])
+def test_whole_prompt_token_by_token_and_in_portions(name, page, dtype):
     """The same sequence three ways: one step; five tokens and then one token a step (through the CUDA graph); portions of
-    changing sizes down to two tokens.  Every position against the plain implementation."""
+    changing sizes down to two tokens.  Every position against the plain implementation; with each configuration's own page
+    size and with another (pages wider than a window, pages of one token)."""
     V = CONFIGS_N[name]["vocab"]
     n = LENGTHS[name]
     toks = random_tokens(n, V, 100 + n)
     seqs = {"w": toks, "d": toks, "p": toks}
-    r = runner(name, dtype, num_pages=3 * (-(-n // PAGE[name])) + 8)
+    r = runner(name, dtype, num_pages=3 * (-(-n // (page or PAGE[name]))) + 8, page_size=page)
     poison(r)
     got = play(r, [{"entries": [("w", toks, list(range(n)))], "end": ["w"]}])
     compare(name, dtype, got, seqs)

@@ -586,3 +586,61 @@ def test_random_configurations(seed, dtype):
             raise AssertionError(f"seed {seed}, request {rid!r} position {pos} ({dtype}): {e}\\n{json.dumps(cj)}") from None
     assert len(over) <= max(1, len(got) // 10), f"seed {seed}: {len(over)} of {len(got)} rows beyond the bound: {over[:8]}"
     r.mgr.check_idle()
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# layers at serving sizes
+# ---------------------------------------------------------------------------------------------------------------------
+@functools.lru_cache(None)
+def _wide_model():
+    """Three layers whose mixers have the sizes of a served model (the stream itself is kept at 512 so that the plain
+    implementation stays quick): 32 heads over a cache row of 192 + 64 with a window, a linear attention with a state of 256 x
+    512 a head, 16 heads over a cache row of 128."""
+    import tiny_nametar as tn
+    cfg = tn._model(512, 1000, 1e-5, 0.5, 20.0, [
+        tn._with(tn._la2(32, 128, 64, 128, 192, window=128, q_rank=256, scaling={"factor": 4.0, "original": 256, "fast": 32.0, "slow": 1.0}), 1024),
+        tn._with(tn._gla(2, 256, 512, 16.0, rank=16), None),
+        tn._with(tn._la(16, 64, 64, 128), 512)])
+    W = make_weights(cfg, 77)
+    return cfg, W, write_model_dir(os.path.join(_tmp.name, "wide"), config_json(cfg), W)
+
+
+@functools.lru_cache(None)
+def _wide_reference():
+    cfg, W, _ = _wide_model()
+    a, b = random_tokens(250, cfg["vocab"], 1), random_tokens(120, cfg["vocab"], 2)
+    with torch.no_grad():
+        return a, b, {"a": pn.forward_sequence(config_json(cfg), W, a).float(), "b": pn.forward_sequence(config_json(cfg), W, b).float()}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixers_at_serving_sizes(dtype):
+    """A 220-token prompt in one step (the prompt kernels at these head counts and row sizes, the window's edge inside the
+    portion, the linear attention in chunks), then a second request's portions behind a cached context beside decoded tokens
+    of the first through the graph."""
+    from mini_sglang_b200.engine.step import ModelRunner
+    cfg, W, d = _wide_model()
+    a, b, ref = _wide_reference()
+    r = ModelRunner.from_model_dir(d, dtype=dtype, page_size=16, num_pages=40, max_reqs=2, max_context_len=1024)
+    poison(r)
+    want_a = [0, 1, 60, 127, 128, 129, 200, 219]
+    steps = [{"entries": [("a", a[:220], want_a)]},
+             {"entries": [("b", b[:80], [0, 79])]},
+             {"entries": [("a", [a[220]], [0]), ("b", b[80:110], [0, 29])]}]
+    steps += [{"entries": [("a", [a[221 + i]], [0]), ("b", [b[110 + i]], [0])]} for i in range(10)]
+    steps += [{"entries": [("a", [a[231 + i]], [0])]} for i in range(19)]
+    got = play(r, steps)
+    assert r.last_step_used_graph
+    over = []
+    for (rid, pos), row in sorted(got.items()):
+        try:
+            row_close(row, ref[rid][pos], dtype, 0.03)
+        except AssertionError as e:
+            if dtype == "bfloat16" and torch.isfinite(row).all():
+                err = (row - ref[rid][pos]).pow(2).mean().sqrt() / ref[rid][pos].pow(2).mean().sqrt()
+                if float(err) < 0.075:
+                    over.append((rid, pos, round(float(err), 3)))
+                    continue
+            raise AssertionError(f"request {rid!r} position {pos} ({dtype}): {e}") from None
+    assert len(over) <= 1, over
+    r.mgr.check_idle()

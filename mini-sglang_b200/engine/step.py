@@ -654,7 +654,7 @@ class ModelRunner:
         self.last_plan = {"graph_key": key, "nsplits": nsplits, "max_split": list(gr.max_split),
                           "even_blocks": [c[0] for c in even_cuts] if even_cuts else None}
         lay = gr.layout
-        if self.device_meta:
+        if self.device_meta and self.mgr.groups:      # a model that keeps no keys has no tables to mirror: the host writes the few fields
             self._meta_on_device(gr, entries, starts, nsplits, b, even_cuts)
         else:
             host, idx = self._pinned_buffer(lay.size)

@@ -644,3 +644,50 @@ def test_mixers_at_serving_sizes(dtype):
             raise AssertionError(f"request {rid!r} position {pos} ({dtype}): {e}") from None
     assert len(over) <= 1, over
     r.mgr.check_idle()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kinds", ["linear only", "latent only", "one layer"])
+def test_models_of_one_kind_of_layer(kinds, dtype):
+    """A model that keeps no keys at all (only states), one that keeps no state and has no window (one cache group), and a
+    model of a single layer: whole, token by token through the graph, in portions."""
+    import tiny_nametar as tn
+    from mini_sglang_b200.engine.step import ModelRunner
+    layers = {"linear only": [tn._with(tn._gla(2, 16, 24, 4.0, rank=4), 48), tn._with(tn._gla(3, 8, 8, 16.0, rank=2), None)],
+              "latent only": [tn._with(tn._la(3, 16, 8, 32), 48), tn._with(tn._la2(2, 8, 8, 12, 24, window=None, q_rank=16), None)],
+              "one layer": [tn._with(tn._la2(4, 8, 8, 8, 40, window=5, scaling=tn.YARN), 32)]}[kinds]
+    cfg = tn._model(64, 50, 1e-5, 0.6, 4.0, layers)
+    cj, W = config_json(cfg), make_weights(cfg, 9)
+    d = write_model_dir(os.path.join(_tmp.name, kinds.replace(" ", "_")), cj, W)
+    n = 45
+    a = random_tokens(n, cfg["vocab"], 3)
+    with torch.no_grad():
+        ref = pn.forward_sequence(cj, W, a).float()
+    r = ModelRunner.from_model_dir(d, dtype=dtype, page_size=4, num_pages=40, max_reqs=2, max_context_len=256)
+    assert len(r.mgr.groups) == {"linear only": 0, "latent only": 1, "one layer": 1}[kinds]
+    poison(r)
+    steps = [{"entries": [("w", a, list(range(n)))], "end": ["w"]}, {"entries": [("d", a[:3], [2])]}]
+    steps += [{"entries": [("d", [t], [0])]} for t in a[3:]]
+    steps += [{"entries": [("p", a[i:i + 7], list(range(len(a[i:i + 7]))))]} for i in range(0, n, 7)]
+    got = play(r, steps)
+    assert r.last_step_used_graph is False and len(got) == 3 * n - 2
+    for (rid, pos), row in sorted(got.items()):
+        try:
+            row_close(row, ref[pos], dtype, 0.04)
+        except AssertionError as e:
+            raise AssertionError(f"{kinds}, request {rid!r} position {pos} ({dtype}): {e}") from None
+    r.mgr.check_idle()
+    if dtype != "float32":
+        return
+    # and through the entry point: the scheduler's admission with no page pool at all / with the prefix tree over a cache whose
+    # rows are keys and values at once (two prompts share their first 24 tokens)
+    del r
+    from mini_sglang_b200 import Engine, EngineArgs
+    prompts = [a[:30], a[:24] + random_tokens(9, cfg["vocab"], 8), a[:7]]
+    eng = Engine(EngineArgs(model=d, dtype=dtype, page_size=4, num_pages=64, max_num_reqs=3, random_seed=0, chunk_size=16,
+                            max_context_len=128, log_level="WARNING"))
+    for _ in range(2):          # the second pass finds the first one's pages in the prefix tree, where the model has one
+        outs = eng.generate(input_ids=prompts, sampling_params={"temperature": 0.0, "max_new_tokens": 6, "ignore_eos": True})
+        for p, o in zip(prompts, outs):
+            assert o["token_ids"] == pn.greedy_generate(cj, W, p, 6), (kinds, o["token_ids"])
+    eng.scheduler.check_idle_invariants()

@@ -691,3 +691,37 @@ def test_models_of_one_kind_of_layer(kinds, dtype):
         for p, o in zip(prompts, outs):
             assert o["token_ids"] == pn.greedy_generate(cj, W, p, 6), (kinds, o["token_ids"])
     eng.scheduler.check_idle_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_two_geometries_in_one_cache_group(dtype):
+    """Two latent attentions over all keys with different head counts and row sizes share a cache group (one block table, one
+    plan of kv splits made from the first one's geometry).  A long context, then portions of a few tokens and single tokens:
+    short runs take the decode kernel with the keys cut into pieces, and which runs are short differs between the two."""
+    import tiny_nametar as tn
+    from mini_sglang_b200.engine.step import ModelRunner
+    cfg = tn._model(64, 50, 1e-5, 0.6, 4.0, [tn._with(tn._la(2, 16, 8, 64), 48), tn._with(tn._la(16, 8, 8, 32), None),
+                                              tn._with(tn._la2(3, 8, 8, 8, 40, window=300, q_rank=16), 32),
+                                              tn._with(tn._la2(12, 8, 8, 8, 24, window=300), None)])
+    cj, W = config_json(cfg), make_weights(cfg, 11)
+    d = write_model_dir(os.path.join(_tmp.name, "two_geometries"), cj, W)
+    n = 420
+    a = random_tokens(n, cfg["vocab"], 4)
+    with torch.no_grad():
+        ref = pn.forward_sequence(cj, W, a).float()
+    r = ModelRunner.from_model_dir(d, dtype=dtype, page_size=16, num_pages=32, max_reqs=2, max_context_len=1024)
+    assert len(r.mgr.groups) == 2
+    poison(r)
+    steps, at = [{"entries": [("a", a[:380], [0, 379])]}], 380
+    for c in (3, 2, 4, 1, 1, 8, 2, 1, 5, 1, 1, 1, 3, 6, 1):
+        steps.append({"entries": [("a", a[at:at + c], list(range(c)))]})
+        at += c
+    assert at == n
+    got = play(r, steps)
+    assert any(max(ns) > 1 for ns in r.last_plan["nsplits"]), "the test wants kv splits"
+    for (rid, pos), row in sorted(got.items()):
+        try:
+            row_close(row, ref[pos], dtype, 0.04)
+        except AssertionError as e:
+            raise AssertionError(f"position {pos} ({dtype}): {e}") from None
+    r.mgr.check_idle()

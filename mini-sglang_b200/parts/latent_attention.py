@@ -97,7 +97,9 @@ class LatentAttention(Mixer):
         self.w_o = f(n["out"]).contiguous()
 
     def cache_need(self):
-        return PagedKVNeed(1, self.D, self.window, q_heads=self.H, shared_kv=True)
+        # every request's keys are cut by themselves: with one kv head for all query heads the decode launch reads a
+        # thirteenth of a grouped-query cache, and dealing the keys out evenly over the blocks has nothing to even out
+        return PagedKVNeed(1, self.D, self.window, q_heads=self.H, shared_kv=True, even_cut=False)
 
     # -- compute -----------------------------------------------------------------------
     def forward(self, x: torch.Tensor, ctx, cache: KVCacheView, writes_cache: bool = True) -> torch.Tensor:

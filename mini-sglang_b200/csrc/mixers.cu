@@ -1556,17 +1556,19 @@ MSGL_API int msgl_group_rms_gate(const float* x, int heads, int d, const float* 
 //   1. gated_chunk_prep_kernel   b_i for every token (a running sum per channel within the chunk)
 //   2. gated_chunk_kv_kernel     U = sum_i diag(2^(b_(L-1) - b_i)) k_i v_i^T                   every chunk by itself
 //   3. gated_chunk_scan_kernel   per request, chunk after chunk: U <- S, S <- diag(2^b_(L-1)) S + U; the state row gets the last S
-//   4. gated_chunk_p_kernel      P[i][j] = sum_c q_i[c] k_j[c] 2^(b_i[c] - b_j[c]) for j <= i  (one exponential a term: every
+//   4. gated_chunk_p_kernel      P[i][j] = sum_c q_i[c] k_j[c] 2^(b_i[c] - b_j[c]) for j <= i, stored by key  (one exponential a term: every
 //                                exponent is <= 0, so nothing overflows however strong the decay)
 //   5. gated_chunk_out_kernel    o_i = (q_i * 2^b_i) S + sum_(j <= i) P[i][j] v_j
 //
-// All products are float32 FMA through shared memory; the results differ from the token-by-token kernel by rounding only.
+// All products are float32 FMA through shared memory (8 x 8 results a thread in the last kernel, 4 x 4 in the second, which
+// was measured slower with the larger tile: its time goes into staging the decayed keys, not into the products); the results
+// differ from the token-by-token kernel by rounding only.
 // ---------------------------------------------------------------------------------------
 struct GatedChunkParams {
     DecayChunkParams d;           // d.decay is not used
     const float* z; const float* z_bias; float inv_tau_log2e; float q_scale;
     float* bcum;                  // [T][heads * dk]
-    float* P;                     // [chunks][heads][64][64]
+    float* P;                     // [chunks][heads][64 keys][64 queries]
 };
 
 __global__ void __launch_bounds__(128) gated_chunk_prep_kernel(const GatedChunkParams p) {
@@ -1693,7 +1695,7 @@ __global__ void __launch_bounds__(256) gated_chunk_p_kernel(const GatedChunkPara
     const int tid = threadIdx.x, ii = tid >> 4, jj = tid & 15;
     const int i = ib * GC_IB + ii;
     if (ib * GC_IB >= L) {          // rows past the chunk's last token
-        for (int m = 0; m < DC_C / 16; ++m) P[(size_t)i * DC_C + jj + 16 * m] = 0.f;
+        for (int m = 0; m < DC_C / 16; ++m) P[(size_t)(jj + 16 * m) * DC_C + i] = 0.f;
         return;
     }
     const int HK = d.heads * d.dk;
@@ -1730,77 +1732,80 @@ __global__ void __launch_bounds__(256) gated_chunk_p_kernel(const GatedChunkPara
 #pragma unroll
     for (int m = 0; m < DC_C / 16; ++m) {
         const int j = jj + 16 * m;
-        P[(size_t)i * DC_C + j] = (m <= ib && j <= i && i < L) ? acc[m] : 0.f;
+        P[(size_t)j * DC_C + i] = (m <= ib && j <= i && i < L) ? acc[m] : 0.f;          // stored by key: the next kernel sums over keys
     }
 }
 
+#define GO_TN 256       // output columns a block of gated_chunk_out_kernel makes
+#define GO_LDA 68       // row length of the left operand's slabs: 16-byte rows, and a column's 64 stores spread over the banks
+// 8 x 32 threads, 8 x 8 results a thread (tokens ty*4.. and 32+ty*4.., columns tx*4.. and 128+tx*4..).  Both products run over
+// slabs of 64 of their inner index m, the left operand stored by m: the chunk's weights by key, then q * 2^b by key channel.
 template <typename T>
 __global__ void __launch_bounds__(256) gated_chunk_out_kernel(const GatedChunkParams p) {
-    __shared__ __align__(16) float As[DC_C][DC_LD];       // v; then slabs of q * 2^b
-    __shared__ __align__(16) float Bs[DC_C][DC_LD];       // the chunk's weights P; then slabs of S
+    extern __shared__ __align__(16) float gsm[];
+    float (*As)[GO_LDA] = reinterpret_cast<float (*)[GO_LDA]>(gsm);                  // [64 m][tokens]
+    float (*Bs)[GO_TN] = reinterpret_cast<float (*)[GO_TN]>(gsm + DC_C * GO_LDA);    // [64 m][columns]
     __shared__ int sh[2];
     const DecayChunkParams& d = p.d;
-    const int chunk = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * 64;
+    const int chunk = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * GO_TN;
     int req, t0, L;
     if (!dc_find_chunk(d, chunk, sh, req, t0, L)) return;
     const int HK = d.heads * d.dk;
     const T* proj = reinterpret_cast<const T*>(d.proj);
-    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    const int tid = threadIdx.x, ty = tid >> 5, tx = tid & 31;
+    float acc[8][8] = {};
+    auto products = [&](int n_m) {
+        for (int m = 0; m < n_m; ++m) {
+            const float4 a0 = *reinterpret_cast<const float4*>(&As[m][ty * 4]), a1 = *reinterpret_cast<const float4*>(&As[m][32 + ty * 4]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&Bs[m][tx * 4]), b1 = *reinterpret_cast<const float4*>(&Bs[m][128 + tx * 4]);
+            const float qa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, sb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int a = 0; a < 8; ++a)
+#pragma unroll
+                for (int b = 0; b < 8; ++b) acc[a][b] = fmaf(qa[a], sb[b], acc[a][b]);
+        }
+    };
+    // ---- O = P V: the weights come stored by key
     const float* P = p.P + ((size_t)chunk * d.heads + h) * DC_C * DC_C;
-    for (int idx = tid; idx < DC_C * 64; idx += 256) {
-        const int j = idx >> 6, nn = idx & 63;
-        Bs[j][nn] = P[idx];                                   // here j is P's row i, nn its column j
+    for (int idx = tid; idx < DC_C * DC_C; idx += 256) As[idx >> 6][idx & 63] = P[idx];
+    for (int idx = tid; idx < DC_C * GO_TN; idx += 256) {
+        const int j = idx / GO_TN, c = idx - j * GO_TN;
         float vv = 0.f;
-        if (j < L && col0 + nn < d.dv) vv = to_f32<T>(proj[(size_t)(t0 + j) * d.stride + d.v_off + h * d.dv + col0 + nn]);
-        As[j][nn] = vv;
+        if (j < L && col0 + c < d.dv) vv = to_f32<T>(proj[(size_t)(t0 + j) * d.stride + d.v_off + h * d.dv + col0 + c]);
+        Bs[j][c] = vv;
     }
     __syncthreads();
-    // ---- O = P V
-    float oacc[4][4] = {};
-    for (int j = 0; j < L; ++j) {
-        float pa[4], vb[4];
-#pragma unroll
-        for (int a = 0; a < 4; ++a) { pa[a] = Bs[ty * 4 + a][j]; vb[a] = As[j][tx * 4 + a]; }
-#pragma unroll
-        for (int a = 0; a < 4; ++a)
-#pragma unroll
-            for (int b = 0; b < 4; ++b) oacc[a][b] = fmaf(pa[a], vb[b], oacc[a][b]);
-    }
+    products(L);
     // ---- O += (Q * 2^b) S, S the state before the chunk
     const float* S = d.U + ((size_t)chunk * d.heads + h) * d.dk * d.dv;
     for (int m0 = 0; m0 < d.dk; m0 += 64) {
         __syncthreads();
         for (int idx = tid; idx < DC_C * 64; idx += 256) {
-            const int i = idx >> 6, m = idx & 63;
+            const int i = idx >> 6, m = idx & 63;            // token i, key channel m0 + m
             float qv = 0.f;
             if (i < L && m0 + m < d.dk) {
                 const int ch = h * d.dk + m0 + m;
                 qv = to_f32<T>(proj[(size_t)(t0 + i) * d.stride + d.q_off + ch]) * p.q_scale * exp2f(p.bcum[(size_t)(t0 + i) * HK + ch]);
             }
-            As[i][m] = qv;
-            float sv = 0.f;                        // here i is the state's row within the slab, m its column
-            if (m0 + i < d.dk && col0 + m < d.dv) sv = S[(size_t)(m0 + i) * d.dv + col0 + m];
-            Bs[i][m] = sv;
+            As[m][i] = qv;
+        }
+        for (int idx = tid; idx < 64 * GO_TN; idx += 256) {
+            const int m = idx / GO_TN, c = idx - m * GO_TN;
+            float sv = 0.f;
+            if (m0 + m < d.dk && col0 + c < d.dv) sv = S[(size_t)(m0 + m) * d.dv + col0 + c];
+            Bs[m][c] = sv;
         }
         __syncthreads();
-        for (int m = 0; m < 64; ++m) {
-            float qa[4], sb[4];
-#pragma unroll
-            for (int a = 0; a < 4; ++a) { qa[a] = As[ty * 4 + a][m]; sb[a] = Bs[m][tx * 4 + a]; }
-#pragma unroll
-            for (int a = 0; a < 4; ++a)
-#pragma unroll
-                for (int b = 0; b < 4; ++b) oacc[a][b] = fmaf(qa[a], sb[b], oacc[a][b]);
-        }
+        products(min(64, d.dk - m0));
     }
 #pragma unroll
-    for (int a = 0; a < 4; ++a) {
-        const int i = ty * 4 + a;
+    for (int a = 0; a < 8; ++a) {
+        const int i = a < 4 ? ty * 4 + a : 32 + ty * 4 + a - 4;
         if (i >= L) continue;
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            const int col = col0 + tx * 4 + b;
-            if (col < d.dv) d.out[(size_t)(t0 + i) * d.heads * d.dv + h * d.dv + col] = oacc[a][b];
+        for (int b = 0; b < 8; ++b) {
+            const int col = col0 + (b < 4 ? tx * 4 + b : 128 + tx * 4 + b - 4);
+            if (col < d.dv) d.out[(size_t)(t0 + i) * d.heads * d.dv + h * d.dv + col] = acc[a][b];
         }
     }
 }
@@ -1816,14 +1821,21 @@ MSGL_API int msgl_gated_decay_attention_chunked(const void* proj, long long stri
     p.d.proj = proj; p.d.stride = stride; p.d.q_off = q_off; p.d.k_off = k_off; p.d.v_off = v_off; p.d.heads = heads; p.d.dk = dk;
     p.d.dv = dv; p.d.B = B; p.d.decay = nullptr; p.d.state = state; p.d.q_start = q_start; p.d.slots = slots; p.d.U = U; p.d.out = out;
     p.z = z; p.z_bias = z_bias; p.inv_tau_log2e = 1.4426950408889634f / tau; p.q_scale = q_scale; p.bcum = bcum; p.P = P;
-    const int n_rt = (dk + 63) / 64, n_ct = (dv + 63) / 64;
+    const int n_rt = (dk + 63) / 64, n_ct = (dv + 63) / 64, n_ot = (dv + GO_TN - 1) / GO_TN;
+    const size_t smem_out = (size_t)DC_C * (GO_LDA + GO_TN) * sizeof(float);
+    static MsglOncePerDevice once;
+    if (once.due()) {
+        cudaFuncSetAttribute(gated_chunk_out_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_out);
+        cudaFuncSetAttribute(gated_chunk_out_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_out);
+        once.mark();
+    }
     gated_chunk_prep_kernel<<<dim3(n_chunks, (heads * dk + 127) / 128), 128, 0, stream>>>(p);
     if (dtype == MSGL_F32) gated_chunk_kv_kernel<float><<<dim3(n_chunks, heads, n_rt * n_ct), 256, 0, stream>>>(p);
     else gated_chunk_kv_kernel<__nv_bfloat16><<<dim3(n_chunks, heads, n_rt * n_ct), 256, 0, stream>>>(p);
     gated_chunk_scan_kernel<<<dim3(B, heads, (dk * dv + 255) / 256), 256, 0, stream>>>(p);
     if (dtype == MSGL_F32) gated_chunk_p_kernel<float><<<dim3(n_chunks, heads, DC_C / GC_IB), 256, 0, stream>>>(p);
     else gated_chunk_p_kernel<__nv_bfloat16><<<dim3(n_chunks, heads, DC_C / GC_IB), 256, 0, stream>>>(p);
-    if (dtype == MSGL_F32) gated_chunk_out_kernel<float><<<dim3(n_chunks, heads, n_ct), 256, 0, stream>>>(p);
-    else gated_chunk_out_kernel<__nv_bfloat16><<<dim3(n_chunks, heads, n_ct), 256, 0, stream>>>(p);
+    if (dtype == MSGL_F32) gated_chunk_out_kernel<float><<<dim3(n_chunks, heads, n_ot), 256, smem_out, stream>>>(p);
+    else gated_chunk_out_kernel<__nv_bfloat16><<<dim3(n_chunks, heads, n_ot), 256, smem_out, stream>>>(p);
     return msgl_check_launch();
 }
